@@ -1,0 +1,80 @@
+/* C entry points of libpurlin (loaded by the Python package with ctypes, usable from C).
+ *
+ * The reference exposes its host API only as C++ templates and a pybind11
+ * module generated at run time (purlin/bindings.py:16-453). This build ships a
+ * prebuilt shared library instead, so the same calls are plain C symbols:
+ * raw device pointers, byte counts, enums as ints, a stream as void*.
+ * Every function returns 0 on success; purlin_last_error() explains a failure.
+ */
+#pragma once
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct PurlinHostContext PurlinHostContext;
+
+const char* purlin_last_error(void);
+int purlin_version(void);
+
+/* ---- layout engine (no GPU needed) ---- */
+size_t purlin_plan_sizeof(void);
+size_t purlin_policy_sizeof(void);
+/* Fills `ws[8]` = {stagingTRSize, lrOffset, signalOffset, gatherOffset, consumedOffset, varLenOffset, totalBytes, packetStride}. */
+int purlin_workspace_layout(int world, size_t stagingTRSize, size_t* ws);
+/* Builds the plan of one call. `sizes`/`outSizes` may be NULL for fixed-size collectives.
+ * `policy` NULL: the tuning table or the built-in default chooses. `policyOut` (optional) receives the choice. */
+int purlin_plan_build(int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
+                      int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace, size_t stagingTRSize,
+                      const void* policy, void* planOut, void* policyOut);
+int purlin_default_policy(int collective, int world, size_t bytes, int dtype, int mode, int multicastAvailable,
+                          size_t stagingTRSize, void* policyOut);
+int purlin_topology(int inLayout, int outLayout, int op, int cyclic, int* out8);
+int purlin_tuning_clear(void);
+int purlin_tuning_add(int collective, int world, uint64_t maxBytes, const void* policy);
+size_t purlin_tuning_size(void);
+
+/* ---- CPU interpreter of a plan: `world` ranks in one process over host memory ---- */
+int purlin_sim_run(int collective, int world, size_t bytes, const size_t* sizesMatrix, int dtype, int reduceOp, int mode,
+                   size_t stagingTRSize, const void* policy, const void* const* srcs, void* const* dsts,
+                   int dropRank, uint32_t* statusOut);
+
+/* ---- contexts ---- */
+/* peerPtrs[world]: base of every rank's symmetric workspace block (peerPtrs[rank] is local).
+ * multicastPtr: NVLS alias of the same block, or 0. Honours PURLIN_DISABLE_MULTIMEM and PURLIN_DISABLE_MULTIMEM_LR. */
+PurlinHostContext* purlin_context_create(int rank, int world, const uint64_t* peerPtrs, uint64_t multicastPtr,
+                                         size_t stagingTRSize, uint64_t timeoutNs, void* stream);
+int purlin_context_destroy(PurlinHostContext* ctx, void* stream);
+int purlin_context_status(PurlinHostContext* ctx, uint32_t* out4, void* stream);   /* synchronises the stream */
+int purlin_context_clear_status(PurlinHostContext* ctx, void* stream);
+int purlin_context_set_timeout(PurlinHostContext* ctx, uint64_t timeoutNs);
+uint64_t purlin_context_seq(PurlinHostContext* ctx, void* stream);                 /* synchronises the stream */
+int purlin_context_has_multicast(PurlinHostContext* ctx);
+const void* purlin_context_device_struct(PurlinHostContext* ctx);                   /* host copy of the device Context */
+size_t purlin_context_sizeof(void);
+
+/* ---- collectives: one kernel launch each, no host synchronisation ---- */
+int purlin_collective(PurlinHostContext* ctx, int collective, const void* src, void* dst, size_t bytes,
+                      const size_t* sizes, const size_t* outSizes, int dtype, int reduceOp, int mode,
+                      const void* policy, void* stream);
+int purlin_all_reduce(PurlinHostContext* ctx, const void* src, void* dst, size_t bytes, int dtype, int reduceOp, int mode, void* stream);
+int purlin_all_gather(PurlinHostContext* ctx, const void* src, void* dst, size_t bytesPerRank, void* stream);
+int purlin_all_gather_v(PurlinHostContext* ctx, const void* src, void* dst, const size_t* bytesList, void* stream);
+int purlin_reduce_scatter(PurlinHostContext* ctx, const void* src, void* dst, size_t bytesPerRankOut, int dtype, int reduceOp, int mode, void* stream);
+int purlin_reduce_scatter_v(PurlinHostContext* ctx, const void* src, void* dst, const size_t* bytesList, int dtype, int reduceOp, int mode, void* stream);
+int purlin_all_to_all(PurlinHostContext* ctx, const void* src, void* dst, size_t bytesPerPeer, void* stream);
+int purlin_all_to_all_v(PurlinHostContext* ctx, const void* src, void* dst, const size_t* inSplits, const size_t* outSplits, void* stream);
+
+/* ---- single-GPU emulation: `world` virtual ranks run as rows of one cooperative grid ---- */
+int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collective, const void* const* srcs, void* const* dsts,
+                          size_t bytes, const size_t* sizesMatrix, int dtype, int reduceOp, int mode, const void* policy,
+                          int absentRank, void* stream);
+
+/* ---- point-to-point copy through the Atom (push or pull over a peer pointer) ---- */
+int purlin_p2p_copy(void* dst, const void* src, size_t bytes, int blocks, int threads, void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,292 @@
+// Stage, Notify And Consume: the device-side executor of a Plan.
+//
+// Behavioural parity with csrc/include/purlin/snac.cuh of the reference:
+//   stage      (237-373)   copy into own staging, last CTA of a chunk notifies
+//   consume    (809-938)   wait for the producer's flag, pull from its staging
+//   reduce     (940-1133)  wait for every rank's flag, reduce the same slice of all
+//   compose    (1984-2072) reduce into the seam, notify, gather every shard
+//   packets    (1163-1955) latency regime: 16-byte flagged packets pushed to peers
+//   arrival    (146-191)   variable-length collectives post and await an arrival packet
+// What is different: the roles, offsets, chunking and flags come from a Plan
+// computed on the host (layout.hpp) instead of template recursion; the same
+// code runs production launches (one rank per GPU, context in kernel
+// parameters) and single-GPU emulation (one grid row per rank, contexts in
+// global memory); every wait is bounded.
+#pragma once
+#include "atom.cuh"
+#include "packet.cuh"
+#include "plan.hpp"
+
+namespace purlin {
+
+// What a device-side collective call needs besides the context
+// (csrc/include/purlin/snac.cuh "SnacArgs" in the reference).
+struct SnacArgs {
+  const unsigned char* src;
+  unsigned char* dst;
+  const Plan* plan;
+};
+
+namespace snac {
+
+struct Frame {
+  uint64_t seq;
+  int half;
+  int bIdx;
+  const unsigned char* src;
+  unsigned char* dst;
+};
+
+PURLIN_D size_t chunkLen(const Step& s, uint32_t k) {
+  const size_t begin = size_t(k) * s.chunkBytes;
+  return s.bytes - begin < s.chunkBytes ? s.bytes - begin : s.chunkBytes;
+}
+PURLIN_D size_t slotOff(const Step& s, uint32_t k) { return size_t(k % s.slots) * s.chunkBytes; }
+
+// thread 0 waits, the whole CTA learns the outcome
+PURLIN_D bool ctaWait(const Context& ctx, const uint64_t* flag, uint64_t value, uint32_t code, int step, int peer, uint32_t k) {
+  int ok = 1;
+  if (threadIdx.x == 0) ok = sig::waitAtLeast(ctx, flag, value, code, step, peer, k) ? 1 : 0;
+  return __syncthreads_and(ok) != 0;
+}
+// thread q waits on flags[q] for every rank q (optionally skipping self)
+PURLIN_D bool ctaWaitAll(const Context& ctx, uint64_t* const* table, int slot, uint64_t value, bool skipSelf,
+                         uint32_t code, int step, uint32_t k) {
+  int ok = 1;
+  const int q = threadIdx.x;
+  if (q < ctx.world && !(skipSelf && q == ctx.rank)) ok = sig::waitAtLeast(ctx, table[slot] + q, value, code, step, q, k) ? 1 : 0;
+  return __syncthreads_and(ok) != 0;
+}
+
+template <class Atom>
+PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
+  const int j = f.bIdx - s.blockBegin, n = s.blockCount;
+  unsigned char* staging = ctx.stagingTR[ctx.rank] + size_t(f.half) * ctx.stagingTRSize + s.dstOff;
+  for (uint32_t k = 0; k < s.chunks; ++k) {
+    if ((s.flags & kFlagCyclic) && k >= s.slots) {
+      // back-pressure: every reader of this slot must have drained its previous tenant
+      const uint64_t need = flagValue(f.seq, k - s.slots);
+      const bool ok = s.peer >= 0
+          ? ctaWait(ctx, ctx.consumedSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k)
+          : ctaWaitAll(ctx, ctx.consumedSignals, ctx.rank, need, (s.flags & kFlagDrainSelf) == 0, kStatusTimeoutSignal, si, k);
+      if (!ok) return false;
+    }
+    superCopy<Atom>(staging + slotOff(s, k), f.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), j, n);
+    __syncthreads();
+    if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
+      const uint64_t v = flagValue(f.seq, k);
+      if (s.peer >= 0) sig::stReleaseSys(ctx.signals[s.peer] + ctx.rank, v);
+      else for (int q = 0; q < ctx.world; ++q) sig::stReleaseSys(ctx.signals[(ctx.rank + q) % ctx.world] + ctx.rank, v);
+    }
+  }
+  return true;
+}
+
+template <class Atom>
+PURLIN_D void local(const Step& s, const Frame& f) {
+  superCopy<Atom>(f.dst + s.dstOff, f.src + s.srcOff, s.bytes, f.bIdx - s.blockBegin, s.blockCount);
+}
+
+// consume (copy) and gather share everything but the flag table
+template <class Atom>
+PURLIN_D bool consume(const Context& ctx, const Step& s, int si, const Frame& f, bool gather) {
+  const int j = f.bIdx - s.blockBegin, n = s.blockCount;
+  const int from = (s.flags & kFlagLocalSource) ? ctx.rank : s.peer;
+  const unsigned char* staging = ctx.stagingTR[from] + size_t(f.half) * ctx.stagingTRSize + s.srcOff;
+  uint64_t* const* table = gather ? ctx.gatherSignals : ctx.signals;
+  for (uint32_t k = 0; k < s.chunks; ++k) {
+    if (!ctaWait(ctx, table[ctx.rank] + s.peer, flagValue(f.seq, k), kStatusTimeoutSignal, si, s.peer, k)) return false;
+    superCopy<Atom>(f.dst + s.dstOff + size_t(k) * s.chunkBytes, staging + slotOff(s, k), chunkLen(s, k), j, n);
+    if (s.flags & kFlagCyclic) {
+      __syncthreads();
+      if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n))
+        sig::stReleaseSys(ctx.consumedSignals[s.peer] + ctx.rank, flagValue(f.seq, k));
+    }
+  }
+  return true;
+}
+
+template <class Atom, DType T, ReduceOp Op>
+PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, const unsigned char** peerPtr) {
+  const int j = f.bIdx - s.blockBegin, n = s.blockCount;
+  const size_t halfOff = size_t(f.half) * ctx.stagingTRSize;
+  for (uint32_t k = 0; k < s.chunks; ++k) {
+    if (!ctaWaitAll(ctx, ctx.signals, ctx.rank, flagValue(f.seq, k), false, kStatusTimeoutSignal, si, k)) return false;
+    const Span sp = partitionAligned(chunkLen(s, k), n, j, kAccessAlign);
+    const size_t in = halfOff + s.srcOff + slotOff(s, k) + sp.offset;
+    if (threadIdx.x < ctx.world) peerPtr[threadIdx.x] = ctx.stagingTR[threadIdx.x] + in;
+    __syncthreads();
+    ReduceArgs a;
+    a.srcs = peerPtr;
+    a.world = ctx.world;
+    a.bytes = sp.bytes;
+    if (s.flags & kFlagMultimemLoad) a.mcSrc = ctx.mcStagingTR + in;
+    const size_t lin = size_t(k) * s.chunkBytes + sp.offset;
+    if (s.flags & kFlagToDst) a.dst = f.dst + s.dstOff + lin;
+    if (s.flags & kFlagToSeam) {
+      const size_t so = halfOff + s.seamOff + slotOff(s, k) + sp.offset;
+      if (s.flags & kFlagMulticastOut) a.mcSeam = ctx.mcStagingTR + so;
+      else a.seam = ctx.stagingTR[ctx.rank] + so;
+    }
+    if (sp.bytes) Atom::template reduce<T, Op>(a);
+    if (s.flags & (kFlagNotifyGather | kFlagCyclic)) {
+      if (s.flags & kFlagMulticastOut) __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
+        const uint64_t v = flagValue(f.seq, k);
+        for (int q = 1; q <= ctx.world; ++q) {
+          const int p = (ctx.rank + q) % ctx.world;
+          if ((s.flags & kFlagNotifyGather) && p != ctx.rank) sig::stReleaseSys(ctx.gatherSignals[p] + ctx.rank, v);
+          if (s.flags & kFlagCyclic) sig::stReleaseSys(ctx.consumedSignals[p] + ctx.rank, v);
+        }
+      }
+    } else {
+      __syncthreads();   // peerPtr is rewritten by the next chunk
+    }
+  }
+  return true;
+}
+
+// ---------------- latency regime ----------------
+PURLIN_D Packet* slotOf(const Context& ctx, int onRank, int fromRank, int half, bool resultHalf) {
+  unsigned char* base = ctx.stagingLR[onRank] + size_t(half) * kPacketEpochBytes + size_t(fromRank) * ctx.packetStride;
+  if (resultHalf) base += ctx.packetStride / 2;
+  return reinterpret_cast<Packet*>(base);
+}
+PURLIN_D Packet* slotOfMulticast(const Context& ctx, int fromRank, int half, bool resultHalf) {
+  unsigned char* base = ctx.mcStagingLR + size_t(half) * kPacketEpochBytes + size_t(fromRank) * ctx.packetStride;
+  if (resultHalf) base += ctx.packetStride / 2;
+  return reinterpret_cast<Packet*>(base);
+}
+
+PURLIN_D void packetPut(const Context& ctx, const Step& s, const Frame& f) {
+  const size_t words = s.bytes / 8, stride = size_t(s.blockCount) * blockDim.x;
+  const uint64_t* src = reinterpret_cast<const uint64_t*>(f.src + s.srcOff);
+  const uint64_t flag = flagValue(f.seq, 0);
+  const size_t first = s.dstOff / 8;
+  for (size_t i = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; i < words; i += stride) {
+    const uint64_t v = src[i];
+    if (s.peer >= 0) {
+      pkt::write(slotOf(ctx, s.peer, ctx.rank, f.half, false) + first + i, v, flag);
+    } else if (s.flags & kFlagMulticastOut) {
+      pkt::writeMulticast(slotOfMulticast(ctx, ctx.rank, f.half, false) + first + i, v, flag);
+    } else {
+      for (int q = 1; q < ctx.world; ++q)
+        pkt::write(slotOf(ctx, (ctx.rank + q) % ctx.world, ctx.rank, f.half, false) + first + i, v, flag);
+    }
+  }
+}
+
+PURLIN_D bool packetGet(const Context& ctx, const Step& s, int si, const Frame& f) {
+  const size_t words = s.bytes / 8, stride = size_t(s.blockCount) * blockDim.x;
+  uint64_t* dst = reinterpret_cast<uint64_t*>(f.dst + s.dstOff);
+  const uint64_t flag = flagValue(f.seq, 0);
+  const Packet* slot = slotOf(ctx, ctx.rank, s.peer, f.half, (s.flags & kFlagResultHalf) != 0) + s.srcOff / 8;
+  bool ok = true;
+  for (size_t i = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; i < words && ok; i += stride) {
+    uint64_t v;
+    ok = pkt::read(ctx, slot + i, flag, v, kStatusTimeoutPacket, si, s.peer);
+    if (ok) dst[i] = v;
+  }
+  return ok;
+}
+
+template <DType T, ReduceOp Op>
+PURLIN_D bool packetReduce(const Context& ctx, const Step& s, int si, const Frame& f) {
+  const size_t words = s.bytes / 8, stride = size_t(s.blockCount) * blockDim.x;
+  const uint64_t* own = reinterpret_cast<const uint64_t*>(f.src + s.seamOff);
+  uint64_t* dst = reinterpret_cast<uint64_t*>(f.dst + s.dstOff);
+  const uint64_t flag = flagValue(f.seq, 0);
+  const size_t first = s.srcOff / 8;
+  bool ok = true;
+  for (size_t i = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; i < words && ok; i += stride) {
+    Acc<T> acc;
+#pragma unroll
+    for (int e = 0; e < ElemTraits<T>::perWord; ++e) acc.v[e] = identity<Op>();
+    const uint64_t mine = own[i];
+    for (int q = 0; q < ctx.world && ok; ++q) {    // ascending rank order: bit-reproducible
+      uint64_t w = mine;
+      if (q != ctx.rank) ok = pkt::read(ctx, slotOf(ctx, ctx.rank, q, f.half, false) + first + i, flag, w, kStatusTimeoutPacket, si, q);
+      accumulate<T, Op>(acc, unpack<T>(w));
+    }
+    if (!ok) break;
+    const uint64_t out = pack<T>(acc);
+    dst[i] = out;
+    if (s.flags & kFlagPublish) {
+      if (s.flags & kFlagMulticastOut) {
+        pkt::writeMulticast(slotOfMulticast(ctx, ctx.rank, f.half, true) + i, out, flag);
+      } else {
+        for (int q = 1; q < ctx.world; ++q)
+          pkt::write(slotOf(ctx, (ctx.rank + q) % ctx.world, ctx.rank, f.half, true) + i, out, flag);
+      }
+    }
+  }
+  return ok;
+}
+
+// ---------------- variable-length arrival handshake ----------------
+PURLIN_D void postArrival(const Context& ctx, const Frame& f, uint64_t payload) {
+  const int q = threadIdx.x;
+  if (q < ctx.world) {
+    Packet* p = reinterpret_cast<Packet*>(ctx.varLenSignals[q]) + f.half * ctx.world + ctx.rank;
+    pkt::write(p, payload, flagValue(f.seq, 0));
+  }
+}
+PURLIN_D bool awaitArrival(const Context& ctx, const Frame& f) {
+  int ok = 1;
+  const int q = threadIdx.x;
+  if (q < ctx.world) {
+    uint64_t v;
+    const Packet* p = reinterpret_cast<const Packet*>(ctx.varLenSignals[ctx.rank]) + f.half * ctx.world + q;
+    ok = pkt::read(ctx, p, flagValue(f.seq, 0), v, kStatusTimeoutArrival, 0, q) ? 1 : 0;
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
+// One CTA's share of a whole collective. `bIdx`/`blocks` are the CTA's index and the
+// grid size of this rank (not of the launch: emulation stacks ranks along grid.y).
+template <class Atom, DType T, ReduceOp Op, bool Reduces>
+PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src, unsigned char* dst,
+                  int bIdx, int blocks, const unsigned char** peerPtr) {
+  Frame f;
+  f.seq = sig::ldRelaxedSys(ctx.seq);
+  f.half = int(f.seq & 1);
+  f.bIdx = bIdx;
+  f.src = src;
+  f.dst = dst;
+  bool ok = !sig::failed(ctx);    // a context that failed stays quiet until the host clears it
+  if (ok && plan.varLenArrival && bIdx == 0) postArrival(ctx, f, plan.payloadBytes);
+  for (int si = 0; si < plan.nSteps && ok; ++si) {
+    const Step& s = plan.steps[si];
+    if (bIdx < s.blockBegin || bIdx >= s.blockBegin + s.blockCount) continue;
+    switch (s.role) {
+      case kRoleStage: ok = stage<Atom>(ctx, s, si, f); break;
+      case kRoleLocal: local<Atom>(s, f); break;
+      case kRoleConsume: ok = consume<Atom>(ctx, s, si, f, false); break;
+      case kRoleGather: ok = consume<Atom>(ctx, s, si, f, true); break;
+      case kRolePacketPut: packetPut(ctx, s, f); break;
+      case kRolePacketGet: ok = __syncthreads_and(packetGet(ctx, s, si, f) ? 1 : 0) != 0; break;
+      case kRoleReduce:
+        if constexpr (Reduces) ok = reduce<Atom, T, Op>(ctx, s, si, f, peerPtr);
+        break;
+      case kRolePacketReduce:
+        if constexpr (Reduces) ok = __syncthreads_and(packetReduce<T, Op>(ctx, s, si, f) ? 1 : 0) != 0;
+        break;
+      default: break;
+    }
+  }
+  if (ok && plan.varLenArrival && bIdx == 0) ok = awaitArrival(ctx, f);
+  // the last CTA out advances the call sequence; the next launch (stream order) reads it
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ctx.exitCounter, 1u) == uint32_t(blocks - 1)) {
+      *ctx.exitCounter = 0;
+      *ctx.seq = f.seq + 1;
+      __threadfence();
+    }
+  }
+}
+
+}  // namespace snac
+}  // namespace purlin

@@ -1,0 +1,345 @@
+// Contexts, the generic SNAC kernel and the host launchers of every collective.
+//
+// Parity: the four templated kernels and their launchers in
+// csrc/include/purlin/host/{allReduce,allGather,reduceScatter,all2all}.cuh and
+// the context set-up of csrc/include/purlin/setup.cuh:35-124 of the reference.
+// One launch per call, no host synchronisation after it, NVTX range around it.
+// A single kernel template executes any Plan; it is instantiated per element
+// type and reduce operator for reductions and once for pure copies.
+#include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+#include <string>
+#include <vector>
+
+#include "purlin/capi.h"
+#include "purlin/layout.hpp"
+#include "purlin/snac.cuh"
+#include "purlin/tuning.hpp"
+
+namespace purlin {
+void setError(const std::string& e);
+bool makeSpec(CollectiveSpec& s, int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
+              int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace);
+bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen);
+}  // namespace purlin
+
+using namespace purlin;
+
+struct PurlinHostContext {
+  Context dev{};
+  WorkspaceLayout ws{};
+  int device = 0;
+  void* localBlock = nullptr;   // seq, exit counter, status, counters
+  bool hasMulticast = false;
+};
+
+namespace {
+
+constexpr int kMaxThreads = 512;
+using Atom = AtomSm100<256, 4, 4>;
+
+#define CUDA_OK(expr)                                                                                   \
+  do {                                                                                                  \
+    cudaError_t e_ = (expr);                                                                            \
+    if (e_ != cudaSuccess) { setError(std::string(#expr) + ": " + cudaGetErrorString(e_)); return 1; } \
+  } while (0)
+
+// Production launch: one rank per GPU, context and plan in kernel parameters.
+template <DType T, ReduceOp Op, bool Reduces>
+__global__ void __launch_bounds__(kMaxThreads, 1)
+snacKernel(const __grid_constant__ Context ctx, const __grid_constant__ Plan plan, const unsigned char* src, unsigned char* dst) {
+  __shared__ const unsigned char* peerPtr[kMaxRanks];
+  snac::run<Atom, T, Op, Reduces>(ctx, plan, src, dst, blockIdx.x, gridDim.x, peerPtr);
+}
+
+// Emulation launch: grid.y virtual ranks on one GPU (cooperative, so all CTAs are resident
+// and may wait on one another), each with its own context, plan and buffers in global memory.
+struct EmuRank {
+  Context ctx;
+  Plan plan;
+  const unsigned char* src;
+  unsigned char* dst;
+  int absent;
+};
+template <DType T, ReduceOp Op, bool Reduces>
+__global__ void __launch_bounds__(kMaxThreads, 1) snacEmuKernel(const EmuRank* ranks) {
+  __shared__ const unsigned char* peerPtr[kMaxRanks];
+  __shared__ alignas(16) unsigned char ctxMem[sizeof(Context)];
+  __shared__ alignas(16) unsigned char planMem[sizeof(Plan)];
+  const EmuRank& me = ranks[blockIdx.y];
+  if (me.absent) return;
+  for (size_t i = threadIdx.x; i < sizeof(Context) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(ctxMem)[i] = reinterpret_cast<const uint32_t*>(&me.ctx)[i];
+  for (size_t i = threadIdx.x; i < sizeof(Plan) / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(planMem)[i] = reinterpret_cast<const uint32_t*>(&me.plan)[i];
+  __syncthreads();
+  const Context& ctx = *reinterpret_cast<const Context*>(ctxMem);
+  const Plan& plan = *reinterpret_cast<const Plan*>(planMem);
+  if (int(blockIdx.x) >= plan.blocks) return;
+  snac::run<Atom, T, Op, Reduces>(ctx, plan, me.src, me.dst, blockIdx.x, plan.blocks, peerPtr);
+}
+
+template <class Atom_>
+__global__ void __launch_bounds__(kMaxThreads, 1) p2pKernel(unsigned char* dst, const unsigned char* src, size_t bytes) {
+  superCopy<Atom_>(dst, src, bytes, blockIdx.x, gridDim.x);
+}
+
+using ProdFn = void (*)(const Context, const Plan, const unsigned char*, unsigned char*);
+using EmuFn = void (*)(const EmuRank*);
+
+template <DType T> ProdFn prodByOp(int op) {
+  switch (ReduceOp(op)) {
+    case ReduceOp::add: return snacKernel<T, ReduceOp::add, true>;
+    case ReduceOp::mul: return snacKernel<T, ReduceOp::mul, true>;
+    default: return snacKernel<T, ReduceOp::max, true>;
+  }
+}
+template <DType T> EmuFn emuByOp(int op) {
+  switch (ReduceOp(op)) {
+    case ReduceOp::add: return snacEmuKernel<T, ReduceOp::add, true>;
+    case ReduceOp::mul: return snacEmuKernel<T, ReduceOp::mul, true>;
+    default: return snacEmuKernel<T, ReduceOp::max, true>;
+  }
+}
+ProdFn prodKernel(const Plan& p) {
+  if (p.consumeOp == int32_t(ConsumeOp::copy)) return snacKernel<DType::fp32, ReduceOp::add, false>;
+  switch (DType(p.dtype)) {
+    case DType::bf16: return prodByOp<DType::bf16>(p.reduceOp);
+    case DType::fp16: return prodByOp<DType::fp16>(p.reduceOp);
+    case DType::fp8e4m3: return prodByOp<DType::fp8e4m3>(p.reduceOp);
+    case DType::fp8e5m2: return prodByOp<DType::fp8e5m2>(p.reduceOp);
+    default: return prodByOp<DType::fp32>(p.reduceOp);
+  }
+}
+EmuFn emuKernel(const Plan& p) {
+  if (p.consumeOp == int32_t(ConsumeOp::copy)) return snacEmuKernel<DType::fp32, ReduceOp::add, false>;
+  switch (DType(p.dtype)) {
+    case DType::bf16: return emuByOp<DType::bf16>(p.reduceOp);
+    case DType::fp16: return emuByOp<DType::fp16>(p.reduceOp);
+    case DType::fp8e4m3: return emuByOp<DType::fp8e4m3>(p.reduceOp);
+    case DType::fp8e5m2: return emuByOp<DType::fp8e5m2>(p.reduceOp);
+    default: return emuByOp<DType::fp32>(p.reduceOp);
+  }
+}
+
+const char* collectiveName(int c) {
+  static const char* names[] = {"allReduce", "allGather", "allGatherV", "reduceScatter", "reduceScatterV", "allToAll", "allToAllV"};
+  return c >= 0 && c < 7 ? names[c] : "collective";
+}
+
+struct NvtxRange {
+  explicit NvtxRange(const char* name, size_t bytes) {
+    nvtxEventAttributes_t a{};
+    a.version = NVTX_VERSION; a.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
+    a.messageType = NVTX_MESSAGE_TYPE_ASCII; a.message.ascii = name;
+    a.payloadType = NVTX_PAYLOAD_TYPE_UNSIGNED_INT64; a.payload.ullValue = bytes;
+    static nvtxDomainHandle_t domain = nvtxDomainCreateA("Purlin");
+    domain_ = domain;
+    nvtxDomainRangePushEx(domain_, &a);
+  }
+  ~NvtxRange() { nvtxDomainRangePop(domain_); }
+  nvtxDomainHandle_t domain_;
+};
+
+int worldOneCopy(const CollectiveSpec& s, const void* src, void* dst, cudaStream_t stream) {
+  // a world of one: every collective is a copy of the rank's own data
+  size_t n = isVariable(s.in) ? s.sizes[0] : s.bytes;
+  if (n && src != dst) CUDA_OK(cudaMemcpyAsync(dst, src, n, cudaMemcpyDeviceToDevice, stream));
+  return 0;
+}
+
+int launchPlan(PurlinHostContext* h, const Plan& plan, const void* src, void* dst, cudaStream_t stream) {
+  ProdFn fn = prodKernel(plan);
+  const int threads = std::min(std::max(plan.threads, 32), kMaxThreads);
+  fn<<<plan.blocks, threads, 0, stream>>>(h->dev, plan, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst));
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t purlin_context_sizeof(void) { return sizeof(Context); }
+
+PurlinHostContext* purlin_context_create(int rank, int world, const uint64_t* peerPtrs, uint64_t multicastPtr,
+                                         size_t stagingTRSize, uint64_t timeoutNs, void* stream) {
+  if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world) { setError("invalid rank or world size"); return nullptr; }
+  if (stagingTRSize < kMinChunkBytes || stagingTRSize > kMaxStagingBytes || stagingTRSize % kAccessAlign) {
+    setError("staging size must be a multiple of 32 bytes between 256 KiB and 256 MiB"); return nullptr;
+  }
+  if (!peerPtrs) { setError("the provider must return one pointer per rank"); return nullptr; }
+  for (int q = 0; q < world; ++q)
+    if (peerPtrs[q] == 0 || peerPtrs[q] % kAccessAlign) { setError("the provider returned a null or unaligned peer pointer"); return nullptr; }
+  if (multicastPtr % kAccessAlign) { setError("the provider returned an unaligned multicast pointer"); return nullptr; }
+  auto* h = new PurlinHostContext();
+  h->ws = workspaceLayout(world, stagingTRSize);
+  if (h->ws.packetStride % kPacketBytes) { delete h; setError("packet stride is not packet aligned"); return nullptr; }
+  cudaGetDevice(&h->device);
+  Context& c = h->dev;
+  c.world = world; c.rank = rank;
+  c.stagingTRSize = stagingTRSize; c.packetStride = h->ws.packetStride;
+  c.timeoutNs = timeoutNs ? timeoutNs : 10ull * 1000 * 1000 * 1000;
+  if (const char* t = std::getenv("PURLIN_TIMEOUT_MS")) c.timeoutNs = std::strtoull(t, nullptr, 10) * 1000000ull;
+  for (int q = 0; q < world; ++q) {
+    unsigned char* base = reinterpret_cast<unsigned char*>(peerPtrs[q]);
+    c.stagingTR[q] = base;
+    c.stagingLR[q] = base + h->ws.lrOffset;
+    c.signals[q] = reinterpret_cast<uint64_t*>(base + h->ws.signalOffset);
+    c.gatherSignals[q] = reinterpret_cast<uint64_t*>(base + h->ws.gatherOffset);
+    c.consumedSignals[q] = reinterpret_cast<uint64_t*>(base + h->ws.consumedOffset);
+    c.varLenSignals[q] = base + h->ws.varLenOffset;
+  }
+  if (multicastPtr && std::getenv("PURLIN_DISABLE_MULTIMEM") == nullptr) {
+    c.mcStagingTR = reinterpret_cast<unsigned char*>(multicastPtr);
+    if (std::getenv("PURLIN_DISABLE_MULTIMEM_LR") == nullptr) c.mcStagingLR = c.mcStagingTR + h->ws.lrOffset;
+  }
+  h->hasMulticast = c.mcStagingTR != nullptr;
+  const size_t localBytes = 256 + size_t(kCounterSlots) * 4;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (cudaMalloc(&h->localBlock, localBytes) != cudaSuccess) { delete h; setError("cudaMalloc of the local counters failed"); return nullptr; }
+  cudaMemsetAsync(h->localBlock, 0, localBytes, s);
+  unsigned char* lb = static_cast<unsigned char*>(h->localBlock);
+  c.seq = reinterpret_cast<uint64_t*>(lb);
+  c.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
+  c.status = reinterpret_cast<uint32_t*>(lb + 128);
+  c.counters = reinterpret_cast<uint32_t*>(lb + 256);
+  if (cudaStreamSynchronize(s) != cudaSuccess) { cudaFree(h->localBlock); delete h; setError("context set-up failed on the stream"); return nullptr; }
+  return h;
+}
+
+int purlin_context_destroy(PurlinHostContext* h, void* stream) {
+  if (!h) return 0;
+  cudaStreamSynchronize(static_cast<cudaStream_t>(stream));   // in-flight collectives still use the counters
+  if (h->localBlock) cudaFree(h->localBlock);
+  delete h;
+  return 0;
+}
+
+int purlin_context_status(PurlinHostContext* h, uint32_t* out4, void* stream) {
+  CUDA_OK(cudaMemcpyAsync(out4, h->dev.status, 16, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  CUDA_OK(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+int purlin_context_clear_status(PurlinHostContext* h, void* stream) {
+  CUDA_OK(cudaMemsetAsync(h->dev.status, 0, 16, static_cast<cudaStream_t>(stream)));
+  CUDA_OK(cudaMemsetAsync(h->dev.exitCounter, 0, 4, static_cast<cudaStream_t>(stream)));
+  CUDA_OK(cudaMemsetAsync(h->dev.counters, 0, size_t(kCounterSlots) * 4, static_cast<cudaStream_t>(stream)));
+  return 0;
+}
+int purlin_context_set_timeout(PurlinHostContext* h, uint64_t timeoutNs) { h->dev.timeoutNs = timeoutNs; return 0; }
+uint64_t purlin_context_seq(PurlinHostContext* h, void* stream) {
+  uint64_t v = 0;
+  cudaMemcpyAsync(&v, h->dev.seq, 8, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  return v;
+}
+int purlin_context_has_multicast(PurlinHostContext* h) { return h->hasMulticast ? 1 : 0; }
+const void* purlin_context_device_struct(PurlinHostContext* h) { return &h->dev; }
+
+int purlin_collective(PurlinHostContext* h, int collective, const void* src, void* dst, size_t bytes,
+                      const size_t* sizes, const size_t* outSizes, int dtype, int reduceOp, int mode,
+                      const void* policy, void* stream) {
+  if (!h) { setError("null context"); return 1; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  CollectiveSpec spec;
+  if (!makeSpec(spec, collective, h->dev.world, h->dev.rank, bytes, sizes, outSizes, dtype, reduceOp, mode, h->hasMulticast, src == dst)) return 1;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16) { setError("buffers must be 16-byte aligned (32 for full speed)"); return 1; }
+  NvtxRange range(collectiveName(collective), isVariable(spec.in) ? dispatchBytes(spec) : bytes);
+  if (h->dev.world == 1) return worldOneCopy(spec, src, dst, s);
+  const bool variable = isVariable(spec.in);
+  if (!variable && bytes == 0) return 0;
+  const Policy* forced = static_cast<const Policy*>(policy);
+  // A two-shot all-reduce larger than the staging half runs as consecutive segments; each segment is a
+  // complete collective on the alternating half, so the next segment's staging overlaps this one's tail.
+  if (spec.type == CollectiveType::allReduce && bytes > h->ws.stagingTRSize) {
+    const size_t seg = roundDown(h->ws.stagingTRSize, size_t(h->dev.world) * kAccessAlign);
+    for (size_t off = 0; off < bytes; off += seg) {
+      CollectiveSpec part = spec;
+      part.bytes = std::min(seg, bytes - off);
+      Plan plan;
+      if (!planFor(part, h->ws, forced, plan, nullptr)) return 1;
+      if (launchPlan(h, plan, static_cast<const unsigned char*>(src) + off, static_cast<unsigned char*>(dst) + off, s)) return 1;
+    }
+    return 0;
+  }
+  Plan plan;
+  if (!planFor(spec, h->ws, forced, plan, nullptr)) return 1;
+  return launchPlan(h, plan, src, dst, s);
+}
+
+int purlin_all_reduce(PurlinHostContext* h, const void* src, void* dst, size_t bytes, int dtype, int reduceOp, int mode, void* stream) {
+  return purlin_collective(h, int(CollectiveType::allReduce), src, dst, bytes, nullptr, nullptr, dtype, reduceOp, mode, nullptr, stream);
+}
+int purlin_all_gather(PurlinHostContext* h, const void* src, void* dst, size_t bytesPerRank, void* stream) {
+  return purlin_collective(h, int(CollectiveType::allGather), src, dst, bytesPerRank, nullptr, nullptr, 0, 0, 0, nullptr, stream);
+}
+int purlin_all_gather_v(PurlinHostContext* h, const void* src, void* dst, const size_t* bytesList, void* stream) {
+  return purlin_collective(h, int(CollectiveType::allGatherV), src, dst, 0, bytesList, nullptr, 0, 0, 0, nullptr, stream);
+}
+int purlin_reduce_scatter(PurlinHostContext* h, const void* src, void* dst, size_t bytesPerRankOut, int dtype, int reduceOp, int mode, void* stream) {
+  return purlin_collective(h, int(CollectiveType::reduceScatter), src, dst, bytesPerRankOut, nullptr, nullptr, dtype, reduceOp, mode, nullptr, stream);
+}
+int purlin_reduce_scatter_v(PurlinHostContext* h, const void* src, void* dst, const size_t* bytesList, int dtype, int reduceOp, int mode, void* stream) {
+  return purlin_collective(h, int(CollectiveType::reduceScatterV), src, dst, 0, bytesList, nullptr, dtype, reduceOp, mode, nullptr, stream);
+}
+int purlin_all_to_all(PurlinHostContext* h, const void* src, void* dst, size_t bytesPerPeer, void* stream) {
+  return purlin_collective(h, int(CollectiveType::allToAll), src, dst, bytesPerPeer, nullptr, nullptr, 0, 0, 0, nullptr, stream);
+}
+int purlin_all_to_all_v(PurlinHostContext* h, const void* src, void* dst, const size_t* inSplits, const size_t* outSplits, void* stream) {
+  return purlin_collective(h, int(CollectiveType::allToAllV), src, dst, 0, inSplits, outSplits, 0, 0, 0, nullptr, stream);
+}
+
+int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collective, const void* const* srcs, void* const* dsts,
+                          size_t bytes, const size_t* sizesMatrix, int dtype, int reduceOp, int mode, const void* policy,
+                          int absentRank, void* stream) {
+  if (world < 2 || world > kMaxRanks) { setError("emulation needs 2..16 virtual ranks"); return 1; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<EmuRank> host(world);
+  int blocks = 1, threads = 32;
+  const bool a2av = collective == int(CollectiveType::allToAllV);
+  for (int r = 0; r < world; ++r) {
+    size_t in[kMaxRanks] = {}, out[kMaxRanks] = {};
+    if (sizesMatrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? sizesMatrix[size_t(r) * world + q] : sizesMatrix[q]; out[q] = a2av ? sizesMatrix[size_t(q) * world + r] : 0; }
+    CollectiveSpec spec;
+    if (!makeSpec(spec, collective, world, r, bytes, sizesMatrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, srcs[r] == dsts[r])) return 1;
+    if (!planFor(spec, ctxs[r]->ws, static_cast<const Policy*>(policy), host[r].plan, nullptr)) return 1;
+    host[r].ctx = ctxs[r]->dev;
+    host[r].src = static_cast<const unsigned char*>(srcs[r]);
+    host[r].dst = static_cast<unsigned char*>(dsts[r]);
+    host[r].absent = r == absentRank ? 1 : 0;
+    blocks = std::max(blocks, host[r].plan.blocks);
+    threads = std::max(threads, host[r].plan.threads);
+  }
+  threads = std::min(threads, kMaxThreads);
+  EmuFn fn = emuKernel(host[0].plan);
+  int perSm = 0, dev = 0, sms = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, threads, 0));
+  if (blocks * world > perSm * sms) { setError("emulated grid does not fit on the GPU at once; use fewer CTAs per rank"); return 1; }
+  EmuRank* devRanks = nullptr;
+  CUDA_OK(cudaMallocAsync(&devRanks, sizeof(EmuRank) * world, s));
+  CUDA_OK(cudaMemcpyAsync(devRanks, host.data(), sizeof(EmuRank) * world, cudaMemcpyHostToDevice, s));
+  CUDA_OK(cudaStreamSynchronize(s));   // `host` is pageable and dies with this frame
+  void* args[] = {&devRanks};
+  CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fn), dim3(blocks, world), dim3(threads), args, 0, s));
+  CUDA_OK(cudaFreeAsync(devRanks, s));
+  return 0;
+}
+
+int purlin_p2p_copy(void* dst, const void* src, size_t bytes, int blocks, int threads, void* stream) {
+  if (bytes % 16 || (reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) % 16) { setError("p2p copy needs 16-byte alignment"); return 1; }
+  blocks = std::min(std::max(blocks, 1), kMaxCtas);
+  threads = std::min(std::max(threads, 32), kMaxThreads);
+  p2pKernel<Atom><<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned char*>(dst), static_cast<const unsigned char*>(src), bytes);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,432 @@
+// Host-only half of libpurlin: the layout engine's C entry points, the tuning
+// table and a CPU interpreter that executes the same Plan the GPU kernels run.
+//
+// The reference has no CPU emulation of its protocol (its multi-rank logic is
+// only exercised on GPUs: csrc/tests/{ar,ag,rs,a2a}.cu). The interpreter here
+// runs every rank of a collective inside one process over host memory, with
+// real flag words, packet flags, last-arrival semantics and cyclic
+// back-pressure, so protocol errors (a wait nobody satisfies, a slot reused too
+// early, a byte produced twice or never) show up without a GPU. A rank can be
+// made absent to check that the others report a time-out instead of hanging.
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "purlin/capi.h"
+#include "purlin/layout.hpp"
+#include "purlin/tuning.hpp"
+
+namespace purlin {
+thread_local std::string g_lastError;
+void setError(const std::string& e) { g_lastError = e; }
+}  // namespace purlin
+
+using namespace purlin;
+
+namespace {
+
+bool fillSpec(CollectiveSpec& s, int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
+              int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace) {
+  if (collective < 0 || collective > int(CollectiveType::allToAllV)) { setError("unknown collective"); return false; }
+  s = specFor(CollectiveType(collective));
+  s.world = world; s.rank = rank; s.bytes = bytes;
+  s.dtype = DType(dtype); s.reduceOp = ReduceOp(reduceOp); s.mode = ReductionMode(mode);
+  s.multicastAvailable = multicastAvailable != 0; s.inPlace = inPlace != 0;
+  if (world < 1 || world > kMaxRanks) { setError("world size must be 1..16"); return false; }
+  const bool v = isVariable(s.in);
+  if (v) {
+    if (!sizes) { setError("variable-length collective needs a size list"); return false; }
+    for (int q = 0; q < world; ++q) s.sizes[q] = sizes[q];
+    if (s.type == CollectiveType::allToAllV) {
+      if (!outSizes) { setError("all-to-all-v needs output splits"); return false; }
+      for (int q = 0; q < world; ++q) s.outSizes[q] = outSizes[q];
+    }
+    for (int q = 0; q < world; ++q)
+      if (s.sizes[q] % kAccessAlign || s.outSizes[q] % kAccessAlign) { setError("every size must be a multiple of 32 bytes"); return false; }
+  } else if (bytes % kAccessAlign) { setError("byte count must be a multiple of 32"); return false; }
+  return true;
+}
+
+}  // namespace
+
+namespace purlin {
+// shared with the CUDA half
+bool makeSpec(CollectiveSpec& s, int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
+              int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace) {
+  return fillSpec(s, collective, world, rank, bytes, sizes, outSizes, dtype, reduceOp, mode, multicastAvailable, inPlace);
+}
+bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen) {
+  std::string err;
+  Policy p = forced ? *forced : selectPolicy(s, ws);
+  bool ok = buildPlan(s, p, ws, plan, err);
+  if (!ok && !forced) {   // a measured band may not fit this call (uneven V sizes): fall back to built-in choices
+    std::string err2;
+    p = defaultPolicy(s, ws);
+    ok = buildPlan(s, p, ws, plan, err2);
+    if (!ok && p.regime == int32_t(Regime::latency)) {
+      p.regime = int32_t(Regime::throughput);
+      ok = buildPlan(s, p, ws, plan, err2);
+    }
+    if (!ok) err = err2;
+  }
+  if (!ok) { setError(err); return false; }
+  if (chosen) *chosen = p;
+  return true;
+}
+}  // namespace purlin
+
+extern "C" {
+
+const char* purlin_last_error(void) { return g_lastError.c_str(); }
+int purlin_version(void) { return 100; }
+size_t purlin_plan_sizeof(void) { return sizeof(Plan); }
+size_t purlin_policy_sizeof(void) { return sizeof(Policy); }
+
+int purlin_workspace_layout(int world, size_t stagingTRSize, size_t* ws) {
+  if (world < 1 || world > kMaxRanks) { setError("world size must be 1..16"); return 1; }
+  const WorkspaceLayout w = workspaceLayout(world, stagingTRSize);
+  ws[0] = w.stagingTRSize; ws[1] = w.lrOffset; ws[2] = w.signalOffset; ws[3] = w.gatherOffset;
+  ws[4] = w.consumedOffset; ws[5] = w.varLenOffset; ws[6] = w.totalBytes; ws[7] = w.packetStride;
+  return 0;
+}
+
+int purlin_plan_build(int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
+                      int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace, size_t stagingTRSize,
+                      const void* policy, void* planOut, void* policyOut) {
+  CollectiveSpec s;
+  if (!fillSpec(s, collective, world, rank, bytes, sizes, outSizes, dtype, reduceOp, mode, multicastAvailable, inPlace)) return 1;
+  const WorkspaceLayout ws = workspaceLayout(world, stagingTRSize);
+  Plan plan;
+  if (!planFor(s, ws, static_cast<const Policy*>(policy), plan, static_cast<Policy*>(policyOut))) return 1;
+  std::memcpy(planOut, &plan, sizeof(plan));
+  return 0;
+}
+
+int purlin_default_policy(int collective, int world, size_t bytes, int dtype, int mode, int multicastAvailable,
+                          size_t stagingTRSize, void* policyOut) {
+  CollectiveSpec s = specFor(CollectiveType(collective));
+  s.world = world; s.bytes = bytes; s.dtype = DType(dtype); s.mode = ReductionMode(mode); s.multicastAvailable = multicastAvailable != 0;
+  for (int q = 0; q < world && q < kMaxRanks; ++q) s.sizes[q] = s.outSizes[q] = bytes;
+  const Policy p = defaultPolicy(s, workspaceLayout(world, stagingTRSize));
+  std::memcpy(policyOut, &p, sizeof(p));
+  return 0;
+}
+
+int purlin_topology(int inLayout, int outLayout, int op, int cyclic, int* out8) {
+  if (!validTriple(DataLayout(inLayout), DataLayout(outLayout), ConsumeOp(op))) { setError("layout pair is not a collective"); return 1; }
+  const Topology t = deriveTopology(DataLayout(inLayout), DataLayout(outLayout), ConsumeOp(op), cyclic != 0);
+  out8[0] = t.perDest; out8[1] = t.perStream; out8[2] = t.variable; out8[3] = t.varLenArrival;
+  out8[4] = t.selfDirect; out8[5] = t.reduceWhole; out8[6] = int(t.notify); out8[7] = int(t.drain);
+  return 0;
+}
+
+int purlin_tuning_clear(void) { TuningTable::global().clear(); return 0; }
+int purlin_tuning_add(int collective, int world, uint64_t maxBytes, const void* policy) {
+  TuningEntry e; e.collective = collective; e.world = world; e.maxBytes = maxBytes; e.policy = *static_cast<const Policy*>(policy);
+  TuningTable::global().add(e);
+  return 0;
+}
+size_t purlin_tuning_size(void) { return TuningTable::global().size(); }
+
+}  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// CPU interpreter
+// ------------------------------------------------------------------------------------------
+namespace {
+
+struct HostPacket { uint64_t data, flag; };
+
+struct SimRank {
+  std::vector<unsigned char> block;   // the symmetric workspace block, same format as on the GPU
+  std::vector<uint32_t> counters;
+  uint64_t seq = 0;
+  Plan plan;
+  const unsigned char* src = nullptr;
+  unsigned char* dst = nullptr;
+  bool absent = false;
+};
+
+float bf16ToF(uint16_t h) { uint32_t u = uint32_t(h) << 16; float f; std::memcpy(&f, &u, 4); return f; }
+uint16_t fToBf16(float f) {
+  uint32_t u; std::memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return uint16_t((u >> 16) | 0x40);
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return uint16_t(u >> 16);
+}
+float halfToF(uint16_t h) {
+  const uint32_t sign = uint32_t(h & 0x8000u) << 16, exp = (h >> 10) & 0x1fu, man = h & 0x3ffu;
+  uint32_t u;
+  if (exp == 0) {
+    if (man == 0) u = sign;
+    else { int e = -1; uint32_t m = man; do { ++e; m <<= 1; } while (!(m & 0x400u)); u = sign | ((127 - 15 - e) << 23) | ((m & 0x3ffu) << 13); }
+  } else if (exp == 31) u = sign | 0x7f800000u | (man << 13);
+  else u = sign | ((exp + 112) << 23) | (man << 13);
+  float f; std::memcpy(&f, &u, 4); return f;
+}
+uint16_t fToHalf(float f) {
+  uint32_t u; std::memcpy(&u, &f, 4);
+  const uint32_t sign = (u >> 16) & 0x8000u;
+  const int32_t exp = int32_t((u >> 23) & 0xff) - 127 + 15;
+  uint32_t man = u & 0x7fffffu;
+  if (((u >> 23) & 0xff) == 0xff) return uint16_t(sign | 0x7c00u | (man ? 0x200u : 0));
+  if (exp >= 31) return uint16_t(sign | 0x7c00u);
+  if (exp <= 0) {
+    if (exp < -10) return uint16_t(sign);
+    man |= 0x800000u;
+    const int shift = 14 - exp;
+    uint32_t r = man >> shift;
+    const uint32_t rem = man & ((1u << shift) - 1), halfway = 1u << (shift - 1);
+    if (rem > halfway || (rem == halfway && (r & 1))) ++r;
+    return uint16_t(sign | r);
+  }
+  uint32_t r = (uint32_t(exp) << 10) | (man >> 13);
+  const uint32_t rem = man & 0x1fffu;
+  if (rem > 0x1000u || (rem == 0x1000u && (r & 1))) ++r;
+  return uint16_t(sign | r);
+}
+
+float combine(ReduceOp op, float a, float b) { return op == ReduceOp::add ? a + b : op == ReduceOp::mul ? a * b : std::fmax(a, b); }
+float identityOf(ReduceOp op) { return op == ReduceOp::add ? 0.f : op == ReduceOp::mul ? 1.f : -INFINITY; }
+
+// out = reduce over ranks (ascending) of srcs[q][0..bytes), fp32 accumulation
+bool reduceHost(DType t, ReduceOp op, const std::vector<const unsigned char*>& srcs, size_t bytes, unsigned char* out0, unsigned char* out1) {
+  const int eb = dtypeBytes(t);
+  if (t != DType::fp32 && t != DType::bf16 && t != DType::fp16) return false;
+  const size_t n = bytes / eb;
+  for (size_t i = 0; i < n; ++i) {
+    float acc = identityOf(op);
+    for (const unsigned char* s : srcs) {
+      float x;
+      if (t == DType::fp32) std::memcpy(&x, s + i * 4, 4);
+      else { uint16_t h; std::memcpy(&h, s + i * 2, 2); x = t == DType::bf16 ? bf16ToF(h) : halfToF(h); }
+      acc = combine(op, acc, x);
+    }
+    unsigned char tmp[4];
+    if (t == DType::fp32) std::memcpy(tmp, &acc, 4);
+    else { const uint16_t h = t == DType::bf16 ? fToBf16(acc) : fToHalf(acc); std::memcpy(tmp, &h, 2); }
+    if (out0) std::memcpy(out0 + i * eb, tmp, eb);
+    if (out1) std::memcpy(out1 + i * eb, tmp, eb);
+  }
+  return true;
+}
+
+struct Agent { int rank, step; uint32_t chunk = 0; size_t word = 0; bool done = false; bool drainedThisChunk = false; };
+
+struct Sim {
+  int W;
+  WorkspaceLayout ws;
+  std::vector<SimRank> ranks;
+  uint32_t status[4] = {0, 0, 0, 0};
+
+  unsigned char* stagingTR(int p, int half) { return ranks[p].block.data() + size_t(half) * ws.stagingTRSize; }
+  HostPacket* slot(int onRank, int fromRank, int half, bool result) {
+    unsigned char* b = ranks[onRank].block.data() + ws.lrOffset + size_t(half) * kPacketEpochBytes + size_t(fromRank) * ws.packetStride;
+    if (result) b += ws.packetStride / 2;
+    return reinterpret_cast<HostPacket*>(b);
+  }
+  uint64_t& signal(int p, int r) { return reinterpret_cast<uint64_t*>(ranks[p].block.data() + ws.signalOffset)[r]; }
+  uint64_t& gatherSignal(int p, int r) { return reinterpret_cast<uint64_t*>(ranks[p].block.data() + ws.gatherOffset)[r]; }
+  uint64_t& consumed(int p, int r) { return reinterpret_cast<uint64_t*>(ranks[p].block.data() + ws.consumedOffset)[r]; }
+  HostPacket* arrival(int p, int half, int r) { return reinterpret_cast<HostPacket*>(ranks[p].block.data() + ws.varLenOffset) + half * W + r; }
+
+  static size_t chunkLen(const Step& s, uint32_t k) { const size_t b = size_t(k) * s.chunkBytes; return std::min<size_t>(s.chunkBytes, s.bytes - b); }
+  static size_t slotOff(const Step& s, uint32_t k) { return size_t(k % s.slots) * s.chunkBytes; }
+
+  // copy a chunk the way `n` CTAs would: each its aligned share, so coverage errors in the split show up
+  static void splitCopy(unsigned char* dst, const unsigned char* src, size_t bytes, int n) {
+    for (int j = 0; j < n; ++j) { const Span sp = partitionAligned(bytes, n, j, kAccessAlign); if (sp.bytes) std::memcpy(dst + sp.offset, src + sp.offset, sp.bytes); }
+  }
+
+  // Advance one agent as far as its waits allow. Returns true if it made progress.
+  bool advance(Agent& a) {
+    SimRank& R = ranks[a.rank];
+    const Step& s = R.plan.steps[a.step];
+    const int r = a.rank, half = int(R.seq & 1);
+    const uint64_t seq = R.seq;
+    bool progressed = false;
+    switch (s.role) {
+      case kRoleStage:
+        while (a.chunk < s.chunks) {
+          const uint32_t k = a.chunk;
+          if ((s.flags & kFlagCyclic) && k >= s.slots) {
+            const uint64_t need = flagValue(seq, k - s.slots);
+            bool ok = true;
+            if (s.peer >= 0) ok = consumed(r, s.peer) >= need;
+            else for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagDrainSelf)) continue; if (consumed(r, q) < need) ok = false; }
+            if (!ok) return progressed;
+          }
+          splitCopy(stagingTR(r, half) + s.dstOff + slotOff(s, k), R.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), s.blockCount);
+          const uint64_t v = flagValue(seq, k);
+          if (s.peer >= 0) signal(s.peer, r) = v; else for (int q = 0; q < W; ++q) signal(q, r) = v;
+          ++a.chunk; progressed = true;
+        }
+        a.done = true; return true;
+      case kRoleLocal:
+        splitCopy(R.dst + s.dstOff, R.src + s.srcOff, s.bytes, s.blockCount);
+        a.done = true; return true;
+      case kRoleConsume:
+      case kRoleGather:
+        while (a.chunk < s.chunks) {
+          const uint32_t k = a.chunk;
+          const uint64_t have = s.role == kRoleGather ? gatherSignal(r, s.peer) : signal(r, s.peer);
+          if (have < flagValue(seq, k)) return progressed;
+          const int from = (s.flags & kFlagLocalSource) ? r : s.peer;
+          splitCopy(R.dst + s.dstOff + size_t(k) * s.chunkBytes, stagingTR(from, half) + s.srcOff + slotOff(s, k), chunkLen(s, k), s.blockCount);
+          if (s.flags & kFlagCyclic) consumed(s.peer, r) = flagValue(seq, k);
+          ++a.chunk; progressed = true;
+        }
+        a.done = true; return true;
+      case kRoleReduce:
+        while (a.chunk < s.chunks) {
+          const uint32_t k = a.chunk;
+          for (int q = 0; q < W; ++q) if (signal(r, q) < flagValue(seq, k)) return progressed;
+          std::vector<const unsigned char*> srcs;
+          for (int q = 0; q < W; ++q) srcs.push_back(stagingTR(q, half) + s.srcOff + slotOff(s, k));
+          const size_t len = chunkLen(s, k), lin = size_t(k) * s.chunkBytes;
+          std::vector<unsigned char> tmp(len);
+          if (!reduceHost(DType(R.plan.dtype), ReduceOp(R.plan.reduceOp), srcs, len, tmp.data(), nullptr)) { status[0] = kStatusBadPlan; a.done = true; return true; }
+          if (s.flags & kFlagToDst) std::memcpy(R.dst + s.dstOff + lin, tmp.data(), len);
+          if (s.flags & kFlagToSeam) {
+            if (s.flags & kFlagMulticastOut) { for (int q = 0; q < W; ++q) std::memcpy(stagingTR(q, half) + s.seamOff + slotOff(s, k), tmp.data(), len); }
+            else std::memcpy(stagingTR(r, half) + s.seamOff + slotOff(s, k), tmp.data(), len);
+          }
+          const uint64_t v = flagValue(seq, k);
+          for (int q = 0; q < W; ++q) {
+            if ((s.flags & kFlagNotifyGather) && q != r) gatherSignal(q, r) = v;
+            if (s.flags & kFlagCyclic) consumed(q, r) = v;
+          }
+          ++a.chunk; progressed = true;
+        }
+        a.done = true; return true;
+      case kRolePacketPut: {
+        const size_t words = s.bytes / 8;
+        const uint64_t flag = flagValue(seq, 0);
+        for (size_t i = 0; i < words; ++i) {
+          uint64_t v; std::memcpy(&v, R.src + s.srcOff + i * 8, 8);
+          if (s.peer >= 0) slot(s.peer, r, half, false)[s.dstOff / 8 + i] = HostPacket{v, flag};
+          else for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagMulticastOut)) continue; slot(q, r, half, false)[s.dstOff / 8 + i] = HostPacket{v, flag}; }
+        }
+        a.done = true; return true;
+      }
+      case kRolePacketGet: {
+        const size_t words = s.bytes / 8;
+        const uint64_t flag = flagValue(seq, 0);
+        const HostPacket* p = slot(r, s.peer, half, (s.flags & kFlagResultHalf) != 0) + s.srcOff / 8;
+        while (a.word < words) {
+          if (p[a.word].flag != flag) return progressed;
+          std::memcpy(R.dst + s.dstOff + a.word * 8, &p[a.word].data, 8);
+          ++a.word; progressed = true;
+        }
+        a.done = true; return true;
+      }
+      case kRolePacketReduce: {
+        const size_t words = s.bytes / 8;
+        const uint64_t flag = flagValue(seq, 0);
+        while (a.word < words) {
+          const size_t i = a.word;
+          uint64_t w[kMaxRanks];
+          for (int q = 0; q < W; ++q) {
+            if (q == r) { std::memcpy(&w[q], R.src + s.seamOff + i * 8, 8); continue; }
+            const HostPacket& p = slot(r, q, half, false)[s.srcOff / 8 + i];
+            if (p.flag != flag) return progressed;
+            w[q] = p.data;
+          }
+          std::vector<const unsigned char*> srcs;
+          for (int q = 0; q < W; ++q) srcs.push_back(reinterpret_cast<const unsigned char*>(&w[q]));
+          uint64_t out = 0;
+          if (!reduceHost(DType(R.plan.dtype), ReduceOp(R.plan.reduceOp), srcs, 8, reinterpret_cast<unsigned char*>(&out), nullptr)) { status[0] = kStatusBadPlan; a.done = true; return true; }
+          std::memcpy(R.dst + s.dstOff + i * 8, &out, 8);
+          if (s.flags & kFlagPublish)
+            for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagMulticastOut)) continue; slot(q, r, half, true)[i] = HostPacket{out, flag}; }
+          ++a.word; progressed = true;
+        }
+        a.done = true; return true;
+      }
+      default: a.done = true; return true;
+    }
+  }
+
+  // One call on every present rank. Returns false (and a status) when some wait can never be satisfied.
+  bool call() {
+    std::vector<Agent> agents;
+    for (int r = 0; r < W; ++r) {
+      if (ranks[r].absent) continue;
+      const int half = int(ranks[r].seq & 1);
+      if (ranks[r].plan.varLenArrival) for (int q = 0; q < W; ++q) *arrival(q, half, r) = HostPacket{ranks[r].plan.payloadBytes, flagValue(ranks[r].seq, 0)};
+      for (int s = 0; s < ranks[r].plan.nSteps; ++s) { Agent a; a.rank = r; a.step = s; agents.push_back(a); }
+    }
+    // steps that share a CTA range run in plan order on the device; keep that order here
+    for (;;) {
+      bool progress = false, allDone = true;
+      for (size_t i = 0; i < agents.size(); ++i) {
+        Agent& a = agents[i];
+        if (a.done) continue;
+        bool blockedByEarlier = false;
+        const Step& s = ranks[a.rank].plan.steps[a.step];
+        for (size_t j = 0; j < i; ++j) {
+          const Agent& b = agents[j];
+          if (b.rank != a.rank || b.done) continue;
+          const Step& t = ranks[b.rank].plan.steps[b.step];
+          if (t.blockBegin < s.blockBegin + s.blockCount && s.blockBegin < t.blockBegin + t.blockCount) { blockedByEarlier = true; break; }
+        }
+        if (!blockedByEarlier && advance(a)) progress = true;
+        if (!a.done) allDone = false;
+      }
+      if (allDone) break;
+      if (!progress) {
+        for (const Agent& a : agents) if (!a.done) {
+          const Step& s = ranks[a.rank].plan.steps[a.step];
+          status[0] = (s.role >= kRolePacketPut) ? kStatusTimeoutPacket : kStatusTimeoutSignal;
+          status[1] = uint32_t(a.step); status[2] = uint32_t(s.peer); status[3] = a.chunk;
+          break;
+        }
+        return false;
+      }
+    }
+    for (int r = 0; r < W; ++r) {
+      if (ranks[r].absent) continue;
+      if (ranks[r].plan.varLenArrival) {
+        const int half = int(ranks[r].seq & 1);
+        for (int q = 0; q < W; ++q) if (arrival(r, half, q)->flag != flagValue(ranks[r].seq, 0)) { status[0] = kStatusTimeoutArrival; status[2] = uint32_t(q); return false; }
+      }
+    }
+    for (int r = 0; r < W; ++r) if (!ranks[r].absent) ++ranks[r].seq;
+    return status[0] == 0;
+  }
+};
+
+}  // namespace
+
+extern "C" int purlin_sim_run(int collective, int world, size_t bytes, const size_t* sizesMatrix, int dtype, int reduceOp, int mode,
+                              size_t stagingTRSize, const void* policy, const void* const* srcs, void* const* dsts,
+                              int dropRank, uint32_t* statusOut) {
+  if (world < 1 || world > kMaxRanks) { setError("world size must be 1..16"); return 1; }
+  Sim sim;
+  sim.W = world;
+  sim.ws = workspaceLayout(world, stagingTRSize);
+  sim.ranks.resize(world);
+  for (int r = 0; r < world; ++r) {
+    SimRank& R = sim.ranks[r];
+    R.block.assign(sim.ws.totalBytes, 0);
+    R.src = static_cast<const unsigned char*>(srcs[r]);
+    R.dst = static_cast<unsigned char*>(dsts[r]);
+    R.absent = r == dropRank;
+    CollectiveSpec s;
+    // sizesMatrix: allGatherV / reduceScatterV: one row [world]; allToAllV: [world][world], row r = what rank r sends
+    size_t in[kMaxRanks] = {}, out[kMaxRanks] = {};
+    const bool a2av = collective == int(CollectiveType::allToAllV);
+    if (sizesMatrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? sizesMatrix[size_t(r) * world + q] : sizesMatrix[q]; out[q] = a2av ? sizesMatrix[size_t(q) * world + r] : 0; }
+    if (!makeSpec(s, collective, world, r, bytes, sizesMatrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, R.src == R.dst)) return 1;
+    if (!planFor(s, sim.ws, static_cast<const Policy*>(policy), R.plan, nullptr)) return 1;
+  }
+  // two calls back to back so both staging halves and growing flag values are exercised
+  bool ok = true;
+  for (int rep = 0; rep < 2 && ok; ++rep) ok = sim.call();
+  if (statusOut) std::memcpy(statusOut, sim.status, sizeof(sim.status));
+  if (!ok && sim.status[0] == 0) sim.status[0] = kStatusTimeoutSignal;
+  return 0;
+}

@@ -1,0 +1,109 @@
+"""Symmetric-memory providers: where the per-rank workspace block and its peer mappings come from.
+
+The reference abstracts this as the ``SymmetricMemoryProvider`` concept with an
+NVSHMEM implementation for C++ (csrc/contrib/symm_mem.cuh:10-59) and torch
+symmetric memory for Python (purlin/__init__.py:73-85).  Three providers exist here:
+
+``torch``     ``torch.distributed._symmetric_memory`` (CUDA VMM + NVLS multicast alias when the fabric offers it)
+``ipc``       the native CUDA-IPC provider of libpurlin (peer mappings only, no multicast); handles travel over the process group
+``emulated``  ``world`` blocks on one GPU, for single-GPU emulation of a multi-rank collective
+
+All return ``(owner, handle, peer_pointers, multicast_pointer)`` where ``owner`` keeps the memory alive.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import List, Tuple
+
+import torch
+
+
+def allocate_symmetric(nbytes: int, device: torch.device, group=None, provider: str | None = None):
+    provider = provider or os.environ.get("PURLIN_PROVIDER", "torch")
+    if provider == "torch":
+        return _torch_provider(nbytes, device, group)
+    if provider == "ipc":
+        return _ipc_provider(nbytes, device, group)
+    raise ValueError(f"unknown symmetric memory provider {provider!r}")
+
+
+def _torch_provider(nbytes: int, device: torch.device, group):
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm_mem
+    if group is None:
+        group = dist.group.WORLD
+    buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=device)
+    buf.zero_()
+    try:
+        hdl = symm_mem.rendezvous(buf, group)
+    except TypeError:
+        hdl = symm_mem.rendezvous(buf, group.group_name)
+    peer_ptrs = [int(p) for p in hdl.buffer_ptrs]
+    mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+    torch.cuda.synchronize(device)
+    dist.barrier(group)   # every rank's zero-fill is complete before any peer writes a flag
+    return buf, hdl, peer_ptrs, mc
+
+
+class _IpcMapping:
+    """Keeps the local allocation and the opened peer mappings alive; closes them on deletion."""
+
+    def __init__(self, lib, local, opened):
+        self.lib, self.local, self.opened = lib, local, opened
+
+    def close(self):
+        for p in self.opened:
+            self.lib.purlin_ipc_close(C.c_void_p(p))
+        self.opened = []
+        if self.local:
+            self.lib.purlin_ipc_free(C.c_void_p(self.local))
+            self.local = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def _ipc_provider(nbytes: int, device: torch.device, group):
+    import torch.distributed as dist
+    from .. import _native
+    lib = _native.cuda()
+    lib.purlin_ipc_export.argtypes = [C.c_void_p, C.c_char_p]
+    lib.purlin_ipc_open.restype = C.c_void_p
+    lib.purlin_ipc_open.argtypes = [C.c_char_p]
+    lib.purlin_ipc_close.argtypes = [C.c_void_p]
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    # a dedicated cudaMalloc block (not a slice of torch's caching allocator), so the handle maps offset 0
+    lib.purlin_ipc_alloc.restype = C.c_void_p
+    lib.purlin_ipc_alloc.argtypes = [C.c_size_t]
+    lib.purlin_ipc_free.argtypes = [C.c_void_p]
+    with torch.cuda.device(device):
+        local = lib.purlin_ipc_alloc(nbytes)
+    if not local:
+        raise RuntimeError("purlin: " + _native.last_error(lib))
+    handle = C.create_string_buffer(64)
+    _native.check(lib, lib.purlin_ipc_export(C.c_void_p(local), handle))
+    handles: List[bytes] = [b""] * world
+    dist.all_gather_object(handles, handle.raw, group=group)
+    peer_ptrs, opened = [], []
+    for q in range(world):
+        if q == rank:
+            peer_ptrs.append(int(local))
+            continue
+        p = lib.purlin_ipc_open(handles[q])
+        if not p:
+            raise RuntimeError("purlin: " + _native.last_error(lib))
+        opened.append(p)
+        peer_ptrs.append(int(p))
+    dist.barrier(group)
+    mapping = _IpcMapping(lib, local, opened)
+    return mapping, mapping, peer_ptrs, 0
+
+
+def allocate_emulated(nbytes: int, world: int, device: torch.device) -> Tuple[list, list]:
+    """``world`` zeroed blocks on one device; every virtual rank sees the same pointer list."""
+    blocks = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+    return blocks, [b.data_ptr() for b in blocks]
