@@ -308,7 +308,22 @@ int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collect
     if (sizesMatrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? sizesMatrix[size_t(r) * world + q] : sizesMatrix[q]; out[q] = a2av ? sizesMatrix[size_t(q) * world + r] : 0; }
     CollectiveSpec spec;
     if (!makeSpec(spec, collective, world, r, bytes, sizesMatrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, srcs[r] == dsts[r])) return 1;
-    if (!planFor(spec, ctxs[r]->ws, static_cast<const Policy*>(policy), host[r].plan, nullptr)) return 1;
+    Policy fitted;
+    const Policy* use = static_cast<const Policy*>(policy);
+    if (!use) {
+      // the built-in policy sizes grids for a whole GPU per rank; here `world` ranks share one
+      int sms = 148;
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctxs[r]->device);
+      const int budget = std::max(sms / world, 2);
+      fitted = selectPolicy(spec, ctxs[r]->ws);
+      fitted.putBlocks = std::min(fitted.putBlocks, world);
+      fitted.gatherBlocks = std::min(fitted.gatherBlocks, world - 1);
+      fitted.localBlocks = 1;
+      fitted.consumeBlocks = std::min(fitted.consumeBlocks, std::max(budget - 2 * world, 1));
+      fitted.lrBlocks = std::min(fitted.lrBlocks, budget);
+      use = &fitted;
+    }
+    if (!planFor(spec, ctxs[r]->ws, use, host[r].plan, nullptr)) return 1;
     host[r].ctx = ctxs[r]->dev;
     host[r].src = static_cast<const unsigned char*>(srcs[r]);
     host[r].dst = static_cast<unsigned char*>(dsts[r]);

@@ -1,0 +1,154 @@
+"""One rank of the multi-GPU correctness run (launched by test_gpu_distributed.py through torch.distributed.run).
+
+Every rank regenerates every peer's seeded input locally, so expected outputs need no communication
+(the approach of csrc/support/purlin/benchmark/data.cuh:46-61 in the reference). Inputs are integers in
+[-2, 2]: exact in every element type and in any summation order, so NVLS results compare bit-exactly too.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import purlin_b200 as purlin  # noqa: E402
+from helpers import AR, AG, AGV, RS, RSV, A2A, A2AV, ELEM, TORCH_DT, expected, in_out_bytes, ints, policy  # noqa: E402
+
+
+def main():
+    rank = int(os.environ["RANK"])
+    world = int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    staging = int(os.environ.get("PURLIN_TEST_STAGING", 8 << 20))
+    h = purlin.initialize(dist.group.WORLD, dev, 100, None, staging_size=staging, timeout_ms=5000)
+    failures = []
+    count = 0
+
+    def case(name, coll, nbytes=0, sizes=None, dtype=0, op=0, mode=0, pol=None, seed=0, reps=2, graph=False):
+        nonlocal count
+        e = ELEM[dtype]
+        for rep in range(reps):
+            ins = []
+            for r in range(world):
+                ib, _ = in_out_bytes(coll, world, r, nbytes, sizes)
+                lo, hi = (1, 2) if op == 1 else (-2, 2)
+                ins.append(ints(ib // e, dtype, seed * 1000 + rep * 100 + r, lo, hi))
+            _, ob = in_out_bytes(coll, world, rank, nbytes, sizes)
+            x = ins[rank].to(dev)
+            out = torch.full((ob // e,), 7.0, device=dev).to(TORCH_DT[dtype])
+            kw = dict(policy=pol)
+
+            def call():
+                if coll == AR:
+                    purlin.all_reduce(x, out, h, None, mode, purlin.ReduceOp(op), **kw)
+                elif coll == AG:
+                    purlin.all_gather(x, out, h, None, **kw)
+                elif coll == AGV:
+                    purlin.all_gather_v(x, out, sizes, h, None, **kw)
+                elif coll == RS:
+                    purlin.reduce_scatter(x, out, h, None, mode, purlin.ReduceOp(op), **kw)
+                elif coll == RSV:
+                    purlin.reduce_scatter_v(x, out, sizes, h, None, mode, purlin.ReduceOp(op), **kw)
+                elif coll == A2A:
+                    purlin.all_to_all(x, out, h, None, **kw)
+                else:
+                    purlin.all_to_all_v(x, out, list(sizes[rank]) + [sizes[q][rank] for q in range(world)], h, None, **kw)
+
+            if graph:
+                g = torch.cuda.CUDAGraph()
+                s = torch.cuda.Stream()
+                with torch.cuda.stream(s):
+                    with torch.cuda.graph(g, stream=s):
+                        call()
+                for _ in range(3):
+                    g.replay()
+            else:
+                call()
+            try:
+                purlin.check(h)
+            except TimeoutError as err:
+                failures.append(f"{name}: {err}")
+                purlin.clear_status(h)
+                return
+            exp = expected(coll, world, rank, ins, nbytes, sizes, dtype, op)
+            if not torch.equal(out.cpu().view(torch.uint8), exp.view(torch.uint8)):
+                bad = (out.cpu().view(torch.uint8) != exp.view(torch.uint8)).nonzero()
+                failures.append(f"{name} rep {rep}: {bad.numel()} bytes differ, first at {int(bad[0]) if bad.numel() else -1}")
+                return
+        count += 1
+
+    mc = h.has_multicast
+    if rank == 0:
+        print(f"world {world} multicast {mc} staging {staging}", flush=True)
+    W = world
+    # all-reduce: every band, forced
+    ar_cases = [("one-shot packets", dict(regime=0, arPath=0, lrBlocks=8), 32 * W * 8),
+                ("two-shot packets", dict(regime=0, arPath=1, lrBlocks=8), 32 * W * 64),
+                ("staged direct", dict(arPath=0, consumeBlocks=16, putBlocks=8), 1 << 20),
+                ("staged composed", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8), 1 << 20),
+                ("staged composed chunked", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=256 << 10), 3 << 20),
+                ("segmented", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=1 << 20), staging * 2 + W * 32 * 8)]
+    for name, kw, n in ar_cases:
+        for dtype in (0, 4, 1):
+            case(f"AR {name} dt{dtype}", AR, nbytes=n, dtype=dtype, pol=policy(**kw))
+        case(f"AR {name} max", AR, nbytes=n, dtype=0, op=2, pol=policy(**kw))
+        case(f"AR {name} deterministic", AR, nbytes=n, dtype=0, mode=1, pol=policy(**kw))
+    if mc:
+        for name, kw, n in (("nvls two-shot", dict(arPath=1, memType=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8), 1 << 20),
+                            ("nvls chunked", dict(arPath=1, memType=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=256 << 10), 4 << 20),
+                            ("nvls packets one-shot", dict(regime=0, arPath=0, lrMulticast=1, lrBlocks=8), 32 * W * 8),
+                            ("nvls packets two-shot", dict(regime=0, arPath=1, lrMulticast=1, lrBlocks=8), 32 * W * 64)):
+            for dtype in (0, 4, 1):
+                case(f"AR {name} dt{dtype}", AR, nbytes=n, dtype=dtype, pol=policy(**kw))
+            case(f"AR {name} max", AR, nbytes=n, dtype=0, op=2, pol=policy(**kw))
+        case("RS nvls", RS, nbytes=1 << 18, dtype=0, pol=policy(memType=1, consumeBlocks=16, putBlocks=8))
+    for coll, cname in ((AG, "AG"), (RS, "RS"), (A2A, "A2A")):
+        for name, kw, n in (("packets", dict(regime=0, lrBlocks=8), 32 * 40), ("staged", dict(), 1 << 19),
+                            ("chunked", dict(chunkBytes=128 << 10), (1 << 20) + 64), ("cyclic", dict(chunkBytes=256 << 10), staging // 2)):
+            case(f"{cname} {name}", coll, nbytes=n, dtype=0, pol=policy(putBlocks=max(8, W), consumeBlocks=max(16, 2 * W), **kw))
+    # default policies over sizes (the built-in table chooses)
+    for n in (32 * W, 8 << 10, 64 << 10, 512 << 10, 4 << 20):
+        for coll, cname in ((AR, "AR"), (AG, "AG"), (RS, "RS"), (A2A, "A2A")):
+            case(f"{cname} default {n}", coll, nbytes=n, dtype=0, reps=1)
+    case("AR default graph", AR, nbytes=64 << 10, dtype=0, reps=1, graph=True)
+    case("AR default graph large", AR, nbytes=2 << 20, dtype=0, reps=1, graph=True)
+    # variable-length
+    g = torch.Generator().manual_seed(7)
+    base = 1 << 16
+    sizes = [int(base * (0.5 + float(torch.rand(1, generator=g)))) // 32 * 32 for _ in range(W)]
+    for coll, cname in ((AGV, "AGV"), (RSV, "RSV")):
+        case(f"{cname} random", coll, sizes=sizes, dtype=0)
+        case(f"{cname} with empty", coll, sizes=[0 if q % 2 else s for q, s in enumerate(sizes)], dtype=0)
+        case(f"{cname} small", coll, sizes=[32 * (q + 1) for q in range(W)], dtype=0)
+    mat = [[int(base * float(torch.rand(1, generator=g))) // 32 * 32 if (r + q) % 3 else 0 for q in range(W)] for r in range(W)]
+    case("A2AV mixed", A2AV, sizes=mat, dtype=0, pol=policy(putBlocks=max(8, W), consumeBlocks=max(16, 2 * W), perStreamThreshold=16384, chunkBytes=32768))
+    case("A2AV default", A2AV, sizes=mat, dtype=0)
+    idle = [[0] * W for _ in range(W)]
+    case("A2AV idle", A2AV, sizes=idle, dtype=0)
+    # back-to-back unsynchronised calls on one context
+    x = torch.ones(1 << 16, device=dev, dtype=torch.bfloat16)
+    out = torch.empty_like(x)
+    for i in range(32):
+        purlin.all_reduce(x, out, h, None)
+    purlin.check(h)
+    if not torch.all(out == W).item():
+        failures.append("back-to-back all-reduce")
+    purlin.finalize(h)
+    purlin.finalize(h)
+    ok = torch.tensor([0 if failures else 1], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    for f in failures:
+        print(f"[rank {rank}] FAIL {f}", flush=True)
+    if rank == 0:
+        print(f"cases passed on rank 0: {count}; all ranks ok: {bool(ok.item())}", flush=True)
+    dist.destroy_process_group()
+    sys.exit(0 if ok.item() else 1)
+
+
+if __name__ == "__main__":
+    main()
