@@ -1,0 +1,214 @@
+"""Message-size sweep of every collective against NCCL, and the tuner that fills the codesign table.
+
+Run with one process per GPU:
+  python -m torch.distributed.run --nnodes=1 --nproc-per-node=8 --master-addr 127.0.0.1 \
+      -m purlin_b200.utils.sweep --collectives ar,ag,rs,a2a --min 8K --max 1G [--tune] [--csv out.csv]
+
+Counterpart of the reference's benchmark binaries (csrc/tests/{ar,ag,rs,a2a}.cu: power-of-two sweep, an
+exact-correctness run before timing, CSV on stdout).  ``--tune`` measures a set of candidate policies
+(one-shot / two-shot packets, staged unicast, NVLS; several chunk sizes and grid sizes) for each size and
+writes the winners as the measured codesign table that ``purlin_b200.tuning`` loads at ``initialize``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+import purlin_b200 as purlin
+from purlin_b200 import _native
+from purlin_b200.utils import bench
+
+NAMES = {"ar": purlin.Collective.ALL_REDUCE, "ag": purlin.Collective.ALL_GATHER, "rs": purlin.Collective.REDUCE_SCATTER,
+         "a2a": purlin.Collective.ALL_TO_ALL}
+
+
+def _policy(**kw):
+    base = dict(regime=1, threads=512, putBlocks=32, localBlocks=8, consumeBlocks=48, gatherBlocks=32, lrBlocks=32, memType=0,
+                mmDepth=4, unroll=4, stageDepth=0, arPath=1, lrMulticast=0, weighted=1, chunkBytes=0, perStreamThreshold=128 << 10)
+    base.update(kw)
+    return _native.Policy.from_dict(base)
+
+
+def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool):
+    """Policies worth measuring for one (collective, size). `nbytes` is the dispatch size."""
+    slot = layout["packet_stride"] // 2
+    out = []
+    lr_blocks = sorted({min(max(-(-nbytes // 4096), 1), 64), min(max(-(-nbytes // 2048), 1), 128), 16, 32})
+    if coll == "ar":
+        if nbytes <= slot:
+            for b in lr_blocks:
+                out.append(("lr1", _policy(regime=0, arPath=0, lrBlocks=b)))
+                if multicast:
+                    out.append(("lr1-mc", _policy(regime=0, arPath=0, lrBlocks=b, lrMulticast=1)))
+        if world > 2 and nbytes <= (slot // 2) * world and nbytes % (world * 32) == 0:
+            for b in (28, 56, 112):
+                out.append(("lr2", _policy(regime=0, arPath=1, lrBlocks=b)))
+                if multicast:
+                    out.append(("lr2-mc", _policy(regime=0, arPath=1, lrBlocks=b, lrMulticast=1)))
+        if nbytes >= 64 << 10:
+            chunks = [0] if nbytes <= 2 << 20 else [c for c in (512 << 10, 2 << 20, 8 << 20) if c < nbytes]
+            for c in chunks:
+                for put, con, gat in ((16, 32, 16), (32, 48, 32), (32, 64, 48)):
+                    if world == 2:
+                        out.append(("tr-direct", _policy(arPath=0, putBlocks=put, consumeBlocks=con + gat, chunkBytes=c)))
+                    out.append(("tr-2shot", _policy(arPath=1, putBlocks=put, consumeBlocks=con, gatherBlocks=gat, chunkBytes=c)))
+                if multicast:
+                    for con, depth in ((16, 4), (32, 4), (32, 8), (64, 4)):
+                        out.append(("nvls", _policy(arPath=1, memType=1, putBlocks=32, consumeBlocks=con, gatherBlocks=32, mmDepth=depth, chunkBytes=c)))
+    else:
+        per_rank_total = nbytes * world
+        if nbytes <= slot:
+            for b in lr_blocks:
+                out.append(("lr", _policy(regime=0, lrBlocks=b)))
+        if per_rank_total >= 64 << 10:
+            chunks = [0] if nbytes <= 1 << 20 else [c for c in (512 << 10, 2 << 20, 4 << 20) if c < nbytes]
+            for c in chunks:
+                for put, con in ((16, 32), (32, 64), (32, 96)):
+                    out.append(("tr", _policy(putBlocks=max(put, world), consumeBlocks=con, chunkBytes=c)))
+                if coll == "rs" and multicast:
+                    out.append(("nvls", _policy(memType=1, putBlocks=32, consumeBlocks=32, chunkBytes=c)))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--collectives", default="ar,ag,rs,a2a")
+    ap.add_argument("--min", default="8K")
+    ap.add_argument("--max", default="256M")
+    ap.add_argument("--factor", type=int, default=8)
+    ap.add_argument("--dtype", default="bf16")
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--runs", type=int, default=20)
+    ap.add_argument("--graph", type=int, default=0)
+    ap.add_argument("--tune", action="store_true")
+    ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--csv", default="")
+    ap.add_argument("--table-out", default="")
+    args = ap.parse_args()
+
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    h = purlin.initialize(dist.group.WORLD, dev, 100, None)
+    td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
+    esz = torch.empty(0, dtype=td).element_size()
+    lo, hi = bench.parse_size(args.min), bench.parse_size(args.max)
+    rows, table = [], []
+    if rank == 0:
+        print(bench.CSV_HEADER, flush=True)
+    for coll in args.collectives.split(","):
+        n = lo
+        while n <= hi:
+            # n = per-rank payload in bytes (all-reduce: whole payload; all-gather: input; others: per-rank total in/out)
+            if coll == "ar":
+                in_b, out_b, disp = n, n, n
+            elif coll == "ag":
+                in_b, out_b, disp = n // world, n, n // world
+            elif coll == "rs":
+                in_b, out_b, disp = n, n // world, n // world
+            else:
+                in_b, out_b, disp = n, n, n // world
+            disp = disp // 32 * 32
+            if coll == "ag":
+                in_b, out_b = disp, disp * world
+            elif coll == "rs":
+                in_b, out_b = disp * world, disp
+            elif coll == "a2a":
+                in_b = out_b = disp * world
+            g = torch.Generator().manual_seed(42 + rank)
+            x = torch.randint(-2, 3, (in_b // esz,), generator=g).to(td).to(dev)
+            out = torch.empty(out_b // esz, dtype=td, device=dev)
+            ref = torch.empty_like(out)
+            total = bench.logical_bytes(coll, n if coll == "ar" else disp, world)
+            runs = args.runs if n <= (64 << 20) else max(args.runs // 4, 3)
+
+            def nccl_call():
+                if coll == "ar":
+                    ref.copy_(x); dist.all_reduce(ref)
+                elif coll == "ag":
+                    dist.all_gather_into_tensor(ref, x)
+                elif coll == "rs":
+                    dist.reduce_scatter_tensor(ref, x)
+                else:
+                    dist.all_to_all_single(ref, x)
+
+            def nccl_timed():
+                if coll == "ar":
+                    dist.all_reduce(ref)   # in place, as NCCL users call it
+                else:
+                    nccl_call()
+
+            def ours(pol=None):
+                if coll == "ar":
+                    purlin.all_reduce(x, out, h, None, policy=pol)
+                elif coll == "ag":
+                    purlin.all_gather(x, out, h, None, policy=pol)
+                elif coll == "rs":
+                    purlin.reduce_scatter(x, out, h, None, policy=pol)
+                else:
+                    purlin.all_to_all(x, out, h, None, policy=pol)
+
+            nccl_call()
+            torch.cuda.synchronize()
+            expect = ref.clone()
+
+            def verify(pol, label):
+                out.fill_(7)
+                ours(pol)
+                purlin.check(h)
+                ok = torch.equal(out, expect)
+                flag = torch.tensor([1 if ok else 0], device=dev)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                if not flag.item() and rank == 0:
+                    print(f"# MISMATCH {coll} {n} {label}", flush=True)
+                return bool(flag.item())
+
+            best = None
+            if args.tune:
+                for label, pol in candidates(coll, world, disp if coll != "ar" else n, h.layout, h.has_multicast):
+                    try:
+                        if not verify(pol, label):
+                            continue
+                        t = bench.measure(lambda: ours(pol), args.warmup, runs, args.graph)
+                    except RuntimeError as e:
+                        if rank == 0:
+                            print(f"# skipped {coll} {n} {label}: {e}", flush=True)
+                        continue
+                    if rank == 0:
+                        print("# " + bench.csv_row(coll, f"cand:{label}:{pol.putBlocks}/{pol.consumeBlocks}/{pol.gatherBlocks}/{pol.lrBlocks}/c{pol.chunkBytes}/d{pol.mmDepth}", world, total, args.dtype, t), flush=True)
+                    if best is None or t.us < best[0].us:
+                        best = (t, label, pol)
+                if best is not None:
+                    table.append({"collective": int(NAMES[coll]), "world": world, "bytes": disp if coll != "ar" else n, "label": best[1], "us": best[0].us, "policy": best[2].as_dict()})
+                    if rank == 0:
+                        print(bench.csv_row(coll, "purlin_b200:" + best[1], world, total, args.dtype, best[0]), flush=True)
+            else:
+                ok = verify(None, "default")
+                t = bench.measure(lambda: ours(None), args.warmup, runs, args.graph)
+                if rank == 0:
+                    print(bench.csv_row(coll, "purlin_b200", world, total, args.dtype, t, 0.0 if ok else 100.0), flush=True)
+                    rows.append((coll, "purlin_b200", n, t.us))
+            if not args.no_nccl:
+                t = bench.measure(nccl_timed, args.warmup, runs, args.graph)
+                if rank == 0:
+                    print(bench.csv_row(coll, "nccl", world, total, args.dtype, t), flush=True)
+            n *= args.factor
+    if args.tune and rank == 0:
+        path = args.table_out or os.path.join("gpurun_out", f"tuning_w{world}.json")
+        os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
+        with open(path, "w") as f:
+            json.dump({"gpu": torch.cuda.get_device_name(), "world": world, "entries": table}, f, indent=1)
+        print(f"# wrote {path}", flush=True)
+    purlin.finalize(h)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
