@@ -2,7 +2,7 @@
 
 Run with one process per GPU:
   python -m torch.distributed.run --nnodes=1 --nproc-per-node=8 --master-addr 127.0.0.1 \
-      -m purlin_b200.utils.sweep --collectives ar,ag,rs,a2a --min 8K --max 1G [--tune] [--csv out.csv]
+      -m purlin_b200.utils.sweep --collectives ar,ag,rs,a2a --min-bytes 8K --max-bytes 1G [--tune] [--csv out.csv]
 
 Counterpart of the reference's benchmark binaries (csrc/tests/{ar,ag,rs,a2a}.cu: power-of-two sweep, an
 exact-correctness run before timing, CSV on stdout).  ``--tune`` measures a set of candidate policies
@@ -78,8 +78,8 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--collectives", default="ar,ag,rs,a2a")
-    ap.add_argument("--min", default="8K")
-    ap.add_argument("--max", default="256M")
+    ap.add_argument("--min-bytes", default="8K")
+    ap.add_argument("--max-bytes", default="256M")
     ap.add_argument("--factor", type=int, default=8)
     ap.add_argument("--dtype", default="bf16")
     ap.add_argument("--warmup", type=int, default=5)
@@ -99,7 +99,7 @@ def main():
     h = purlin.initialize(dist.group.WORLD, dev, 100, None)
     td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
     esz = torch.empty(0, dtype=td).element_size()
-    lo, hi = bench.parse_size(args.min), bench.parse_size(args.max)
+    lo, hi = bench.parse_size(args.min_bytes), bench.parse_size(args.max_bytes)
     rows, table = [], []
     if rank == 0:
         print(bench.CSV_HEADER, flush=True)
