@@ -87,20 +87,27 @@ struct AtomSm100 {
   static constexpr int MM_DEPTH = MmDepth;
   static constexpr int GMEM_ACCESS_ALIGNMENT_BYTES = int(kAccessAlign);
 
-  // One CTA copies `bytes` (a multiple of 16; 32 gives the widest accesses).
-  static PURLIN_D void copy(unsigned char* dst, const unsigned char* src, size_t bytes) {
+  // One CTA copies `bytes` (a multiple of 16; 32 gives the widest accesses). `unroll` = 32-byte accesses in
+  // flight per thread (4 or 8): bytes in flight per CTA = threads x unroll x 32.
+  static PURLIN_D void copy(unsigned char* dst, const unsigned char* src, size_t bytes, int unroll = Unroll) {
+    if (unroll >= 8) copyImpl<8>(dst, src, bytes);
+    else copyImpl<4>(dst, src, bytes);
+  }
+
+  template <int U>
+  static PURLIN_D void copyImpl(unsigned char* dst, const unsigned char* src, size_t bytes) {
     const int tid = threadIdx.x, nt = blockDim.x;
     const bool wide = ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 31u) == 0;
     size_t done = 0;
     if (wide) {
       const size_t n = bytes / 32;
       size_t i = tid;
-      for (; i + size_t(Unroll - 1) * nt < n; i += size_t(Unroll) * nt) {
-        Vec32 v[Unroll];
+      for (; i + size_t(U - 1) * nt < n; i += size_t(U) * nt) {
+        Vec32 v[U];
 #pragma unroll
-        for (int u = 0; u < Unroll; ++u) v[u] = ld32(src + (i + size_t(u) * nt) * 32);
+        for (int u = 0; u < U; ++u) v[u] = ld32(src + (i + size_t(u) * nt) * 32);
 #pragma unroll
-        for (int u = 0; u < Unroll; ++u) st32(dst + (i + size_t(u) * nt) * 32, v[u]);
+        for (int u = 0; u < U; ++u) st32(dst + (i + size_t(u) * nt) * 32, v[u]);
       }
       for (; i < n; i += nt) st32(dst + i * 32, ld32(src + i * 32));
       done = n * 32;
@@ -112,40 +119,88 @@ struct AtomSm100 {
     for (size_t i = done + tid; i < bytes; i += nt) dst[i] = src[i];
   }
 
-  // One CTA reduces `bytes` (a multiple of 16) of every rank's slice.
+  // One CTA reduces `bytes` (a multiple of 16) of every rank's slice. `mmDepth` = multimem loads in flight per
+  // thread on the NVLS path (1, 2, 4 or 8).
   template <DType T, ReduceOp Op>
-  static PURLIN_D void reduce(const ReduceArgs& a) {
-    const int tid = threadIdx.x, nt = blockDim.x;
-    const size_t n = a.bytes / 16;
+  static PURLIN_D void reduce(const ReduceArgs& a, int mmDepth = MmDepth) {
     if constexpr (MultimemReducible<T, Op>::value) {
       if (a.mcSrc != nullptr) {
-        size_t i = tid;
-        for (; i + size_t(MmDepth - 1) * nt < n; i += size_t(MmDepth) * nt) {
-          Vec16 v[MmDepth];
-#pragma unroll
-          for (int d = 0; d < MmDepth; ++d) v[d] = multimemLdReduce<T, Op>(a.mcSrc + (i + size_t(d) * nt) * 16);
-#pragma unroll
-          for (int d = 0; d < MmDepth; ++d) emit(a, (i + size_t(d) * nt) * 16, v[d]);
-        }
-        for (; i < n; i += nt) emit(a, i * 16, multimemLdReduce<T, Op>(a.mcSrc + i * 16));
+        if (mmDepth >= 8) reduceMultimem<T, Op, 8>(a);
+        else if (mmDepth >= 4) reduceMultimem<T, Op, 4>(a);
+        else if (mmDepth >= 2) reduceMultimem<T, Op, 2>(a);
+        else reduceMultimem<T, Op, 1>(a);
         return;
       }
     }
-    constexpr int kBatch = 8;   // peers loaded before any is consumed
+    // eight 16-byte loads in flight per thread: peers-per-batch x vectors-per-iteration = 8
+    if (a.world <= 2) reduceUnicast<T, Op, 2>(a);
+    else if (a.world <= 4) reduceUnicast<T, Op, 4>(a);
+    else reduceUnicast<T, Op, 8>(a);
+  }
+
+  template <DType T, ReduceOp Op, int D>
+  static PURLIN_D void reduceMultimem(const ReduceArgs& a) {
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const size_t n = a.bytes / 16;
+    size_t i = tid;
+    for (; i + size_t(D - 1) * nt < n; i += size_t(D) * nt) {
+      Vec16 v[D];
+#pragma unroll
+      for (int d = 0; d < D; ++d) v[d] = multimemLdReduce<T, Op>(a.mcSrc + (i + size_t(d) * nt) * 16);
+#pragma unroll
+      for (int d = 0; d < D; ++d) emit(a, (i + size_t(d) * nt) * 16, v[d]);
+    }
+    for (; i < n; i += nt) emit(a, i * 16, multimemLdReduce<T, Op>(a.mcSrc + i * 16));
+  }
+
+  // Worlds of at most 8 ranks: every peer's copy of U = 8 / WB consecutive vectors is requested before any is
+  // consumed (8 loads of 16 bytes in flight per thread); accumulation stays in ascending rank order.
+  // Larger worlds take peers in batches of 8 with one vector per iteration.
+  template <DType T, ReduceOp Op, int WB>
+  static PURLIN_D void reduceUnicast(const ReduceArgs& a) {
+    constexpr int U = 8 / WB;
+    const int tid = threadIdx.x, nt = blockDim.x;
+    const size_t n = a.bytes / 16;
+    if (a.world <= WB) {
+      for (size_t i0 = tid; i0 < n; i0 += size_t(U) * nt) {
+        Vec16 v[U][WB];
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+#pragma unroll
+          for (int b = 0; b < WB; ++b)
+            if (b < a.world && i0 + size_t(u) * nt < n) v[u][b] = ld16(a.srcs[b] + (i0 + size_t(u) * nt) * 16);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (i0 + size_t(u) * nt >= n) break;
+          Acc<T> lo, hi;
+#pragma unroll
+          for (int e = 0; e < ElemTraits<T>::perWord; ++e) lo.v[e] = hi.v[e] = identity<Op>();
+#pragma unroll
+          for (int b = 0; b < WB; ++b)
+            if (b < a.world) {
+              accumulate<T, Op>(lo, unpack<T>(uint64_t(v[u][b].x[0]) | (uint64_t(v[u][b].x[1]) << 32)));
+              accumulate<T, Op>(hi, unpack<T>(uint64_t(v[u][b].x[2]) | (uint64_t(v[u][b].x[3]) << 32)));
+            }
+          const uint64_t w0 = pack<T>(lo), w1 = pack<T>(hi);
+          emit(a, (i0 + size_t(u) * nt) * 16, Vec16{{uint32_t(w0), uint32_t(w0 >> 32), uint32_t(w1), uint32_t(w1 >> 32)}});
+        }
+      }
+      return;
+    }
     for (size_t i = tid; i < n; i += nt) {
       Acc<T> lo, hi;
 #pragma unroll
       for (int e = 0; e < ElemTraits<T>::perWord; ++e) lo.v[e] = hi.v[e] = identity<Op>();
-      for (int q0 = 0; q0 < a.world; q0 += kBatch) {
-        Vec16 v[kBatch];
+      for (int q0 = 0; q0 < a.world; q0 += 8) {
+        Vec16 v[8];
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (q0 + u < a.world) v[u] = ld16(a.srcs[q0 + u] + i * 16);
+        for (int b = 0; b < 8; ++b)
+          if (q0 + b < a.world) v[b] = ld16(a.srcs[q0 + b] + i * 16);
 #pragma unroll
-        for (int u = 0; u < kBatch; ++u)
-          if (q0 + u < a.world) {
-            accumulate<T, Op>(lo, unpack<T>(uint64_t(v[u].x[0]) | (uint64_t(v[u].x[1]) << 32)));
-            accumulate<T, Op>(hi, unpack<T>(uint64_t(v[u].x[2]) | (uint64_t(v[u].x[3]) << 32)));
+        for (int b = 0; b < 8; ++b)
+          if (q0 + b < a.world) {
+            accumulate<T, Op>(lo, unpack<T>(uint64_t(v[b].x[0]) | (uint64_t(v[b].x[1]) << 32)));
+            accumulate<T, Op>(hi, unpack<T>(uint64_t(v[b].x[2]) | (uint64_t(v[b].x[3]) << 32)));
           }
       }
       const uint64_t w0 = pack<T>(lo), w1 = pack<T>(hi);
@@ -164,13 +219,13 @@ struct AtomSm100 {
 // Grid-level copy: a set of CTAs splits one region and each copies its share
 // (the behaviour of superCopy, csrc/include/purlin/transfer.cuh:9-46).
 template <class Atom>
-PURLIN_D void superCopy(unsigned char* dst, const unsigned char* src, size_t bytes, int part, int parts) {
+PURLIN_D void superCopy(unsigned char* dst, const unsigned char* src, size_t bytes, int part, int parts, int unroll = 4) {
   const size_t units = bytes / kAccessAlign, tail = bytes - units * kAccessAlign;
   const size_t base = units / size_t(parts), rem = units % size_t(parts), p = size_t(part);
   const size_t begin = (p * base + (p < rem ? p : rem)) * kAccessAlign;
   size_t len = (base + (p < rem ? 1 : 0)) * kAccessAlign;
   if (part == parts - 1) len += tail;
-  if (len) Atom::copy(dst + begin, src + begin, len);
+  if (len) Atom::copy(dst + begin, src + begin, len, unroll);
 }
 
 }  // namespace purlin

@@ -35,6 +35,8 @@ struct Frame {
   int bIdx;
   const unsigned char* src;
   unsigned char* dst;
+  int unroll;
+  int mmDepth;
 };
 
 PURLIN_D size_t chunkLen(const Step& s, uint32_t k) {
@@ -71,7 +73,7 @@ PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
           : ctaWaitAll(ctx, ctx.consumedSignals, ctx.rank, need, (s.flags & kFlagDrainSelf) == 0, kStatusTimeoutSignal, si, k);
       if (!ok) return false;
     }
-    superCopy<Atom>(staging + slotOff(s, k), f.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), j, n);
+    superCopy<Atom>(staging + slotOff(s, k), f.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), j, n, f.unroll);
     __syncthreads();
     if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
       const uint64_t v = flagValue(f.seq, k);
@@ -84,7 +86,7 @@ PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
 
 template <class Atom>
 PURLIN_D void local(const Step& s, const Frame& f) {
-  superCopy<Atom>(f.dst + s.dstOff, f.src + s.srcOff, s.bytes, f.bIdx - s.blockBegin, s.blockCount);
+  superCopy<Atom>(f.dst + s.dstOff, f.src + s.srcOff, s.bytes, f.bIdx - s.blockBegin, s.blockCount, f.unroll);
 }
 
 // consume (copy) and gather share everything but the flag table
@@ -96,7 +98,7 @@ PURLIN_D bool consume(const Context& ctx, const Step& s, int si, const Frame& f,
   uint64_t* const* table = gather ? ctx.gatherSignals : ctx.signals;
   for (uint32_t k = 0; k < s.chunks; ++k) {
     if (!ctaWait(ctx, table[ctx.rank] + s.peer, flagValue(f.seq, k), kStatusTimeoutSignal, si, s.peer, k)) return false;
-    superCopy<Atom>(f.dst + s.dstOff + size_t(k) * s.chunkBytes, staging + slotOff(s, k), chunkLen(s, k), j, n);
+    superCopy<Atom>(f.dst + s.dstOff + size_t(k) * s.chunkBytes, staging + slotOff(s, k), chunkLen(s, k), j, n, f.unroll);
     if (s.flags & kFlagCyclic) {
       __syncthreads();
       if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n))
@@ -128,7 +130,7 @@ PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, 
       if (s.flags & kFlagMulticastOut) a.mcSeam = ctx.mcStagingTR + so;
       else a.seam = ctx.stagingTR[ctx.rank] + so;
     }
-    if (sp.bytes) Atom::template reduce<T, Op>(a);
+    if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth);
     if (s.flags & (kFlagNotifyGather | kFlagCyclic)) {
       if (s.flags & kFlagMulticastOut) __threadfence_system();
       __syncthreads();
@@ -254,6 +256,8 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
   f.bIdx = bIdx;
   f.src = src;
   f.dst = dst;
+  f.unroll = plan.unroll;
+  f.mmDepth = plan.mmDepth;
   bool ok = !sig::failed(ctx);    // a context that failed stays quiet until the host clears it
   if (ok && plan.varLenArrival && bIdx == 0) postArrival(ctx, f, plan.payloadBytes);
   for (int si = 0; si < plan.nSteps && ok; ++si) {

@@ -64,13 +64,13 @@ inline Policy defaultPolicy(const CollectiveSpec& s, const WorkspaceLayout& ws) 
   const int W = s.world;
   const uint64_t n = dispatchBytes(s);
   const uint64_t slotPayload = ws.packetStride / 2;
-  p.threads = 512;
-  p.unroll = 4;
+  p.threads = 256;
+  p.unroll = 8;
   p.mmDepth = 4;
   p.weighted = 1;
   p.perStreamThreshold = std::min<uint64_t>(256ull << 10, slotPayload);
   const bool nvls = s.multicastAvailable && s.mode == ReductionMode::nonDeterministic;
-  auto lrBlocks = [&](uint64_t bytes) { return int(std::min<uint64_t>(std::max<uint64_t>(ceilDiv(bytes, uint64_t(p.threads) * 8), 1), 64)); };
+  auto lrBlocks = [&](uint64_t bytes) { return int(std::min<uint64_t>(std::max<uint64_t>(ceilDiv(bytes, uint64_t(p.threads) * 8), 1), 128)); };
   switch (s.type) {
     case CollectiveType::allReduce: {
       const uint64_t oneShotMax = W <= 2 ? (1ull << 20) : W <= 4 ? (128ull << 10) : (64ull << 10);
@@ -85,7 +85,7 @@ inline Policy defaultPolicy(const CollectiveSpec& s, const WorkspaceLayout& ws) 
         p.regime = int32_t(Regime::throughput);
         p.arPath = int32_t(W <= 2 ? AllReducePath::direct : AllReducePath::composed);
         p.memType = int32_t(nvls && W > 2 ? MemType::multimem : MemType::unicast);
-        p.threads = 512;
+        p.threads = 256;
         p.putBlocks = 32; p.consumeBlocks = p.memType == int32_t(MemType::multimem) ? 32 : 48; p.gatherBlocks = 32;
         p.chunkBytes = n <= (4ull << 20) ? 0 : n <= (64ull << 20) ? (2ull << 20) : (8ull << 20);
       }

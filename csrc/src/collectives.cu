@@ -14,6 +14,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 #include <vector>
 
 #include "purlin/capi.h"
@@ -36,11 +37,14 @@ struct PurlinHostContext {
   int device = 0;
   void* localBlock = nullptr;   // seq, exit counter, status, counters
   bool hasMulticast = false;
+  // plans of fixed-size calls under the table/default policy, keyed by (collective, bytes, dtype, op, mode, in-place)
+  std::unordered_map<uint64_t, Plan> planCache;
+  size_t planCacheTableSize = 0;
 };
 
 namespace {
 
-constexpr int kMaxThreads = 512;
+constexpr int kMaxThreads = 256;   // 255 registers per thread: room for 8 wide accesses in flight
 using Atom = AtomSm100<256, 4, 4>;
 
 #define CUDA_OK(expr)                                                                                   \
@@ -267,6 +271,20 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
       if (launchPlan(h, plan, static_cast<const unsigned char*>(src) + off, static_cast<unsigned char*>(dst) + off, s)) return 1;
     }
     return 0;
+  }
+  if (!forced && !variable && bytes < (1ull << 40)) {
+    // the layout engine is deterministic in these inputs: build each plan once
+    if (h->planCacheTableSize != TuningTable::global().size()) { h->planCache.clear(); h->planCacheTableSize = TuningTable::global().size(); }
+    const uint64_t key = (uint64_t(bytes) << 16) ^ (uint64_t(collective) << 12) ^ (uint64_t(dtype) << 8) ^ (uint64_t(reduceOp) << 4) ^
+                         (uint64_t(mode) << 1) ^ uint64_t(src == dst);
+    auto it = h->planCache.find(key);
+    if (it == h->planCache.end()) {
+      Plan fresh;
+      if (!planFor(spec, h->ws, nullptr, fresh, nullptr)) return 1;
+      if (h->planCache.size() > 4096) h->planCache.clear();
+      it = h->planCache.emplace(key, fresh).first;
+    }
+    return launchPlan(h, it->second, src, dst, s);
   }
   Plan plan;
   if (!planFor(spec, h->ws, forced, plan, nullptr)) return 1;

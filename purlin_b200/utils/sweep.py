@@ -28,8 +28,8 @@ NAMES = {"ar": purlin.Collective.ALL_REDUCE, "ag": purlin.Collective.ALL_GATHER,
 
 
 def _policy(**kw):
-    base = dict(regime=1, threads=512, putBlocks=32, localBlocks=8, consumeBlocks=48, gatherBlocks=32, lrBlocks=32, memType=0,
-                mmDepth=4, unroll=4, stageDepth=0, arPath=1, lrMulticast=0, weighted=1, chunkBytes=0, perStreamThreshold=128 << 10)
+    base = dict(regime=1, threads=256, putBlocks=32, localBlocks=8, consumeBlocks=48, gatherBlocks=32, lrBlocks=32, memType=0,
+                mmDepth=4, unroll=8, stageDepth=0, arPath=1, lrMulticast=0, weighted=1, chunkBytes=0, perStreamThreshold=128 << 10)
     base.update(kw)
     return _native.Policy.from_dict(base)
 
