@@ -1,0 +1,31 @@
+"""MoE routing, dispatch (+permute) and combine (+weighted sum) against PyTorch references."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def test_moe_world_of_one():
+    sys.path.insert(0, HERE)
+    from moe_worker import run
+    fails = run(0, 1, torch.device("cuda", 0))
+    assert not fails, fails
+
+
+@pytest.mark.multigpu
+def test_moe_all_gpus():
+    n = torch.cuda.device_count()
+    n = 8 if n >= 8 else 4 if n >= 4 else 2
+    env = dict(os.environ)
+    env.setdefault("NCCL_NVLS_ENABLE", "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+           "--master-addr", "127.0.0.1", "--master-port", "29585", os.path.join(HERE, "moe_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    sys.stdout.write(res.stdout[-3000:])
+    sys.stderr.write(res.stderr[-3000:])
+    assert res.returncode == 0
