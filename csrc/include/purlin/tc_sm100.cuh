@@ -34,9 +34,10 @@ PURLIN_D void mbarArrive(uint32_t bar) {
 }
 PURLIN_D bool mbarTryWait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
+  // cluster-scope acquire: the arrival may come from the other CTA of a pair
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
@@ -65,6 +66,45 @@ PURLIN_D void tmaPrefetchDescriptor(const CUtensorMap* map) {
 }
 PURLIN_D void fenceProxyAsync() { asm volatile("fence.proxy.async;" ::: "memory"); }
 
+// ---- CTA pairs (cluster of two): the pair shares one 256-row MMA; CTA 0 issues it ----
+PURLIN_D uint32_t clusterCtaRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+// address of the same shared-memory offset inside CTA `rank` of the cluster
+PURLIN_D uint32_t mapToCta(uint32_t smemAddress, uint32_t rank) {
+  uint32_t out;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smemAddress), "r"(rank));
+  return out;
+}
+PURLIN_D void clusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+PURLIN_D void mbarArriveCluster(uint32_t clusterBarAddress) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(clusterBarAddress) : "memory");
+}
+// tile load of one CTA of a pair; the transaction bytes are credited to a barrier that may live in the other CTA
+PURLIN_D void tmaLoad2dPair(uint32_t smemDst, const CUtensorMap* map, int x, int y, uint32_t clusterBarAddress) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smemDst), "l"(map), "r"(clusterBarAddress), "r"(x), "r"(y) : "memory");
+}
+PURLIN_D void tmemAllocPair(uint32_t smemResult, uint32_t columns) {   // one whole warp in each CTA of the pair
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemResult), "r"(columns) : "memory");
+}
+PURLIN_D void tmemRelinquishPair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+PURLIN_D void tmemDeallocPair(uint32_t taddr, uint32_t columns) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+// 256 x n x 16 MMA across the pair: each CTA supplies its 128 rows of A and its half of B's columns
+PURLIN_D void mmaPair(uint32_t tmemD, uint64_t aDesc, uint64_t bDesc, uint32_t iDesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmemD), "l"(aDesc), "l"(bDesc), "r"(iDesc), "r"(accumulate) : "memory");
+}
+PURLIN_D void mmaCommitPair(uint32_t clusterBarAddress) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(clusterBarAddress) : "memory");
+}
+
 // ---- TMEM ----
 PURLIN_D void tmemAlloc(uint32_t smemResult, uint32_t columns) {   // whole warp
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smemResult), "r"(columns) : "memory");
@@ -85,9 +125,9 @@ PURLIN_D uint64_t smemDescSw128(uint32_t smemByteAddr) {
   const uint32_t hi = (1024u >> 4) | (1u << 14) | (2u << 29);
   return uint64_t(lo) | (uint64_t(hi) << 32);
 }
-// bf16 x bf16 -> fp32, both operands K-major, M = 128, N = n (multiple of 16, at most 256).
-PURLIN_D uint32_t instrDescBf16(uint32_t n) {
-  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
+// bf16 x bf16 -> fp32, both operands K-major, M = 128 (one CTA) or 256 (a CTA pair), N = n (multiple of 16, at most 256).
+PURLIN_D uint32_t instrDescBf16(uint32_t n, uint32_t m = 128u) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // ---- MMA ----

@@ -27,6 +27,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -106,7 +107,7 @@ PURLIN_D float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 PURLIN_D float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 PURLIN_D float silu(float x) { return x / (1.f + __expf(-x)); }
 
-// order in which row blocks are visited
+// order in which (CTAS x 128)-row blocks are visited
 template <int COMM>
 PURLIN_D int rowBlockOf(const Params& p, int mIdx) {
   if constexpr (COMM == kCommAG) {
@@ -122,14 +123,37 @@ PURLIN_D int rowBlockOf(const Params& p, int mIdx) {
   }
 }
 
-template <int EPI, int COMM>
+// Tile t -> (row-block index, column block). Fused variants walk a row block's columns first (blocks become
+// usable in arrival order). The plain GEMM walks bands of kGroupM row blocks, rows fastest inside a band, so the
+// tiles in flight at one time share a few A blocks and a few B blocks and the working set stays inside L2.
+constexpr int kGroupM = 8;
+template <int COMM>
+PURLIN_D void tileCoord(const Params& p, int t, int& mIdx, int& nBlk) {
+  if constexpr (COMM == kCommNone) {
+    const int perBand = kGroupM * p.tilesN;
+    const int band = t / perBand, within = t - band * perBand;
+    const int first = band * kGroupM;
+    const int rows = p.tilesM - first < kGroupM ? p.tilesM - first : kGroupM;
+    mIdx = first + within % rows;
+    nBlk = within / rows;
+  } else {
+    mIdx = t / p.tilesN;
+    nBlk = t % p.tilesN;
+  }
+}
+
+// CTAS = 1: every CTA owns 128 x bn tiles. CTAS = 2: a cluster of two CTAs owns 256 x bn tiles; each CTA loads its
+// 128 rows of A and its half of B's columns, CTA 0 issues one 256-row MMA for the pair (cta_group::2), so every
+// byte of B crosses L2 -> shared memory once per 256 rows instead of once per 128.
+template <int EPI, int COMM, int CTAS>
 __global__ void __launch_bounds__(COMM == kCommAG ? kThreadsComm : kThreadsPlain, 1)
 gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smemRaw[];
   const uint32_t rawAddr = tc::smemAddr(smemRaw);
   const uint32_t base = (rawAddr + 1023u) & ~1023u;          // swizzled tiles need 1024-byte alignment
   unsigned char* smem = smemRaw + (base - rawAddr);
-  const int stageBytes = kABytes + p.bn * kBK * 2;
+  const int bnLocal = p.bn / CTAS;                           // B columns this CTA keeps in shared memory
+  const int stageBytes = kABytes + bnLocal * kBK * 2;
   const uint32_t barBase = base + uint32_t(p.stages) * stageBytes;
   // barrier block: full[stages], empty[stages], tmemFull[2], tmemEmpty[2], then the TMEM base word and the abort word
   auto fullBar = [&](int s) { return barBase + 8u * s; };
@@ -141,41 +165,53 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
   volatile int* abortWord = reinterpret_cast<volatile int*>(words + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t ctaRank = CTAS == 2 ? tc::clusterCtaRank() : 0u;
+  const int pairIdx = blockIdx.x / CTAS, numPairs = gridDim.x / CTAS;
   const uint64_t epoch = (COMM != kCommNone) ? sig::ldRelaxedSys(p.epoch) + 1 : 1;
   const int parity = int(epoch & 1);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) { tc::mbarInit(fullBar(s), 1); tc::mbarInit(emptyBar(s), 1); }
-    for (int a = 0; a < 2; ++a) { tc::mbarInit(tmemFullBar(a), 1); tc::mbarInit(tmemEmptyBar(a), kEpiWarps); }
+    for (int a = 0; a < 2; ++a) { tc::mbarInit(tmemFullBar(a), 1); tc::mbarInit(tmemEmptyBar(a), kEpiWarps * CTAS); }
     *abortWord = 0;
     tc::mbarFenceInit();
     tc::tmaPrefetchDescriptor(&maps.a);
     tc::tmaPrefetchDescriptor(&maps.b);
   }
-  if (warp == 1) { tc::tmemAlloc(tc::smemAddr(words), kTmemCols); tc::tmemRelinquish(); }
+  if (warp == 1) {
+    if constexpr (CTAS == 2) { tc::tmemAllocPair(tc::smemAddr(words), kTmemCols); tc::tmemRelinquishPair(); }
+    else { tc::tmemAlloc(tc::smemAddr(words), kTmemCols); tc::tmemRelinquish(); }
+  }
   tc::fenceBeforeThreadSync();
-  __syncthreads();
+  if constexpr (CTAS == 2) tc::clusterSync(); else __syncthreads();   // the pair's barriers exist before any remote arrival
   tc::fenceAfterThreadSync();
   const uint32_t tmemBase = *tmemBaseWord;
+  // the barrier block of CTA 0 and of CTA 1 as seen from this CTA (cluster addresses)
+  const uint32_t leaderBars = CTAS == 2 ? tc::mapToCta(barBase, 0) : barBase;
+  const uint32_t peerBars = CTAS == 2 ? tc::mapToCta(barBase, 1) : barBase;
+  (void)peerBars;
 
-  const int numTiles = p.tilesM * p.tilesN;
+  const int numTiles = p.tilesM * p.tilesN;                  // tilesM counts (CTAS x 128)-row blocks
   const int kBlocks = (p.K + kBK - 1) / kBK;
 
   if (warp == 0) {
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
-      uint32_t it = 0;
+      uint32_t st = 0, ph = 0;          // ring position and its phase
       bool ok = true;
-      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x) {
-        const int mIdx = t / p.tilesN, nBlk = t % p.tilesN;
-        const int mBlk = rowBlockOf<COMM>(p, mIdx);
+      for (int t = pairIdx; t < numTiles && ok; t += numPairs) {
+        int mIdx, nBlk;
+        tileCoord<COMM>(p, t, mIdx, nBlk);
+        const int mBlk = rowBlockOf<COMM>(p, mIdx) * CTAS + int(ctaRank);      // this CTA's 128-row block
+        const int bRow = nBlk * p.bn + int(ctaRank) * bnLocal;
         const CUtensorMap* aMap = &maps.a;
         int aRow = mBlk * kBM;
         if constexpr (COMM == kCommAG) {
           if (parity) aMap = &maps.a1;
-          if (mBlk / p.blocksPerRank == p.rank) {
+          const int perRank = p.blocksPerRank * CTAS;
+          if (mBlk / perRank == p.rank) {
             aMap = &maps.aLocal;                       // own rows come straight from the caller's tensor
-            aRow = (mBlk % p.blocksPerRank) * kBM;
+            aRow = (mBlk % perRank) * kBM;
           } else {
             // rows pushed by a peer: wait for the block's flag, then order those generic-proxy writes
             // before this thread's async-proxy reads (TMA)
@@ -184,56 +220,74 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
             tc::fenceProxyAsync();
           }
         }
-        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
-          ok = tc::mbarWait(emptyBar(s), ph ^ 1, abortWord, p.timeoutNs);
+        for (int kb = 0; kb < kBlocks; ++kb) {
+          ok = tc::mbarWait(emptyBar(st), ph ^ 1, abortWord, p.timeoutNs);
           if (!ok) { recordTimeout(p, 1, t, kb); break; }
-          const uint32_t sA = base + uint32_t(s) * stageBytes, sB = sA + kABytes;
-          tc::mbarExpectTx(fullBar(s), uint32_t(stageBytes));
-          tc::tmaLoad2d(sA, aMap, kb * kBK, aRow, fullBar(s));
-          tc::tmaLoad2d(sB, &maps.b, kb * kBK, nBlk * p.bn, fullBar(s));
+          const uint32_t sA = base + st * uint32_t(stageBytes), sB = sA + kABytes;
+          if constexpr (CTAS == 2) {
+            // both CTAs' bytes are credited to CTA 0's barrier; CTA 0 announces the total
+            const uint32_t leaderFull = leaderBars + 8u * st;
+            if (ctaRank == 0) tc::mbarExpectTx(fullBar(st), uint32_t(2 * stageBytes));
+            tc::tmaLoad2dPair(sA, aMap, kb * kBK, aRow, leaderFull);
+            tc::tmaLoad2dPair(sB, &maps.b, kb * kBK, bRow, leaderFull);
+          } else {
+            tc::mbarExpectTx(fullBar(st), uint32_t(stageBytes));
+            tc::tmaLoad2d(sA, aMap, kb * kBK, aRow, fullBar(st));
+            tc::tmaLoad2d(sB, &maps.b, kb * kBK, bRow, fullBar(st));
+          }
+          if (++st == uint32_t(p.stages)) { st = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ------------------------------- MMA issuer -------------------------------
-    if (lane == 0) {
-      const uint32_t idesc = tc::instrDescBf16(uint32_t(p.bn));
-      uint32_t it = 0, accIt = 0;
+    // ------------------------------- MMA issuer (CTA 0 of a pair) -------------------------------
+    if (lane == 0 && ctaRank == 0) {
+      const uint32_t idesc = tc::instrDescBf16(uint32_t(p.bn), uint32_t(kBM * CTAS));
+      // descriptors differ only in their 14-bit start address: keep the constant halves out of the loop
+      const uint64_t descA0 = tc::smemDescSw128(base), descB0 = tc::smemDescSw128(base + kABytes);
+      const uint32_t stageStep = uint32_t(stageBytes) >> 4;
+      uint32_t st = 0, ph = 0, accIt = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++accIt) {
+      for (int t = pairIdx; t < numTiles && ok; t += numPairs, ++accIt) {
         const int a = accIt & 1;
         const uint32_t aph = (accIt >> 1) & 1;
-        ok = tc::mbarWait(tmemEmptyBar(a), aph ^ 1, abortWord, p.timeoutNs);   // epilogue drained this accumulator
+        ok = tc::mbarWait(tmemEmptyBar(a), aph ^ 1, abortWord, p.timeoutNs);   // epilogues drained this accumulator
         if (!ok) { recordTimeout(p, 2, t, 0); break; }
         tc::fenceAfterThreadSync();
         const uint32_t tmemD = tmemBase + uint32_t(a) * kAccStride;
-        for (int kb = 0; kb < kBlocks; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t ph = (it / p.stages) & 1;
-          ok = tc::mbarWait(fullBar(s), ph, abortWord, p.timeoutNs);
+        for (int kb = 0; kb < kBlocks; ++kb) {
+          ok = tc::mbarWait(fullBar(st), ph, abortWord, p.timeoutNs);
           if (!ok) { recordTimeout(p, 3, t, kb); break; }
           tc::fenceAfterThreadSync();
-          const uint32_t sA = base + uint32_t(s) * stageBytes, sB = sA + kABytes;
+          const uint64_t da = descA0 + uint64_t(st * stageStep), db = descB0 + uint64_t(st * stageStep);
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            tc::mma(tmemD, tc::smemDescSw128(sA + k * 32), tc::smemDescSw128(sB + k * 32), idesc, uint32_t((kb | k) != 0));
-          tc::mmaCommit(emptyBar(s));            // the stage is free once these MMAs have read it
+          for (int k = 0; k < kBK / 16; ++k) {
+            if constexpr (CTAS == 2) tc::mmaPair(tmemD, da + 2 * k, db + 2 * k, idesc, uint32_t((kb | k) != 0));
+            else tc::mma(tmemD, da + 2 * k, db + 2 * k, idesc, uint32_t((kb | k) != 0));
+          }
+          // the stage is free (in both CTAs) once these MMAs have read it
+          if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (p.stages + st)); tc::mmaCommitPair(peerBars + 8u * (p.stages + st)); }
+          else tc::mmaCommit(emptyBar(st));
+          if (++st == uint32_t(p.stages)) { st = 0; ph ^= 1; }
         }
-        if (ok) tc::mmaCommit(tmemFullBar(a));   // the accumulator is complete once every MMA of the tile is done
+        if (ok) {   // the accumulator is complete once every MMA of the tile is done
+          if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (2 * p.stages + a)); tc::mmaCommitPair(peerBars + 8u * (2 * p.stages + a)); }
+          else tc::mmaCommit(tmemFullBar(a));
+        }
       }
     }
   } else if (warp < 2 + kEpiWarps) {
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;                // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
+    const int perRank = p.blocksPerRank * CTAS;  // 128-row blocks per rank
     uint32_t accIt = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < numTiles && ok; t += gridDim.x, ++accIt) {
+    for (int t = pairIdx; t < numTiles && ok; t += numPairs, ++accIt) {
       const int a = accIt & 1;
       const uint32_t aph = (accIt >> 1) & 1;
-      const int mIdx = t / p.tilesN, nBlk = t % p.tilesN;
-      const int mBlk = rowBlockOf<COMM>(p, mIdx);
+      int mIdx, nBlk;
+      tileCoord<COMM>(p, t, mIdx, nBlk);
+      const int mBlk = rowBlockOf<COMM>(p, mIdx) * CTAS + int(ctaRank);
       const int n0 = nBlk * p.bn;
       ok = tc::mbarWait(tmemFullBar(a), aph, abortWord, p.timeoutNs);
       ok = __all_sync(0xffffffffu, ok);
@@ -248,19 +302,19 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
       size_t slotStride = 0;
       bool reduceOwn = false;
       if constexpr (COMM == kCommRS) {
-        dstRank = mBlk / p.blocksPerRank;
-        rowInShard = row - dstRank * p.blocksPerRank * kBM;
+        dstRank = mBlk / perRank;
+        rowInShard = row - dstRank * perRank * kBM;
         reduceOwn = dstRank == p.rank && p.world > 1;
         if (reduceOwn) {
           // every peer's partial tile (this row quarter) must have landed
           int good = 1;
           if (lane < p.world && lane != p.rank) {
-            const uint64_t* f = p.tileReady[p.rank] + ((size_t(lane) * p.blocksPerRank + (mBlk % p.blocksPerRank)) * p.tilesN + nBlk) * 4 + quarter;
+            const uint64_t* f = p.tileReady[p.rank] + ((size_t(lane) * perRank + (mBlk % perRank)) * p.tilesN + nBlk) * 4 + quarter;
             good = waitFlag(f, epoch, abortWord, p.timeoutNs) ? 1 : 0;
           }
           ok = __all_sync(0xffffffffu, good);
           if (!ok) { if (lane == 0) recordTimeout(p, 6, t, 0); break; }
-          slotStride = size_t(p.blocksPerRank) * kBM * p.N;
+          slotStride = size_t(perRank) * kBM * p.N;
           partialBase = p.partialBuf[p.rank] + size_t(parity) * p.partialParityStride + size_t(rowInShard) * p.N;
         }
       }
@@ -311,7 +365,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           } else {
             __nv_bfloat16* out = (dstRank == p.rank)
                 ? p.C + size_t(rowInShard) * p.ldc + col      // world of one: plain store
-                : p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride + (size_t(p.rank) * p.blocksPerRank * kBM + rowInShard) * p.N + col;
+                : p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride + (size_t(p.rank) * perRank * kBM + rowInShard) * p.N + col;
 #pragma unroll
             for (int g = 0; g < 4; ++g)
               if (col + g * 8 + 8 <= p.N)
@@ -329,16 +383,19 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           }
         }
       }
-      // hand the accumulator back to the MMA warp
+      // hand the accumulator back to the MMA warp (of CTA 0)
       tc::fenceBeforeThreadSync();
       __syncwarp();
-      if (lane == 0) tc::mbarArrive(tmemEmptyBar(a));
+      if (lane == 0) {
+        if constexpr (CTAS == 2) tc::mbarArriveCluster(leaderBars + 8u * (2 * p.stages + 2 + a));
+        else tc::mbarArrive(tmemEmptyBar(a));
+      }
       if constexpr (COMM == kCommRS) {
         if (dstRank != p.rank) {
           // this warp's 32 rows of the tile are in the peer's memory: publish them
           __syncwarp();
           if (lane == 0) {
-            uint64_t* f = p.tileReady[dstRank] + ((size_t(p.rank) * p.blocksPerRank + (mBlk % p.blocksPerRank)) * p.tilesN + nBlk) * 4 + quarter;
+            uint64_t* f = p.tileReady[dstRank] + ((size_t(p.rank) * perRank + (mBlk % perRank)) * p.tilesN + nBlk) * 4 + quarter;
             sig::stReleaseSys(f, epoch);
           }
         }
@@ -348,14 +405,15 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
     // ------------------------------- communication warps (all-gather push) -------------------------------
     if constexpr (COMM == kCommAG) {
       const int ct = threadIdx.x - 32 * (2 + kEpiWarps), cn = 32 * kCommWarps;
+      const int perRank = p.blocksPerRank * CTAS;
       const size_t blockBytes = size_t(kBM) * p.K * 2;
-      const int items = (p.world - 1) * p.blocksPerRank * p.pushParts;
+      const int items = (p.world - 1) * perRank * p.pushParts;
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int unit = item / p.pushParts, part = item % p.pushParts;
-        const int peer = (p.rank + 1 + unit / p.blocksPerRank) % p.world, b = unit % p.blocksPerRank;
+        const int peer = (p.rank + 1 + unit / perRank) % p.world, b = unit % perRank;
         const Span sp = partitionAligned(blockBytes, p.pushParts, part, kAccessAlign);
         const unsigned char* src = reinterpret_cast<const unsigned char*>(p.localA) + size_t(b) * blockBytes + sp.offset;
-        unsigned char* dst = reinterpret_cast<unsigned char*>(p.gatherBuf[peer]) + size_t(parity) * p.gatherParityBytes + (size_t(p.rank) * p.blocksPerRank + b) * blockBytes + sp.offset;
+        unsigned char* dst = reinterpret_cast<unsigned char*>(p.gatherBuf[peer]) + size_t(parity) * p.gatherParityBytes + (size_t(p.rank) * perRank + b) * blockBytes + sp.offset;
         const size_t n = sp.bytes / 32;
         size_t i = ct;
         for (; i + 3 * size_t(cn) < n; i += 4 * size_t(cn)) {
@@ -368,7 +426,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
         for (; i < n; i += cn) st32(dst + i * 32, ld32(src + i * 32));
         asm volatile("bar.sync 1, %0;" ::"r"(cn) : "memory");
         if (ct == 0 && sig::lastArrival(p.pushCounters + unit, uint32_t(p.pushParts)))
-          sig::stReleaseSys(p.rowReady[peer] + size_t(p.rank) * p.blocksPerRank + b, epoch);
+          sig::stReleaseSys(p.rowReady[peer] + size_t(p.rank) * perRank + b, epoch);
       }
     }
   }
@@ -376,8 +434,11 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
   // ------------------------------- teardown -------------------------------
   if (*abortWord) __nanosleep(20000);   // let copies already in flight land before shared memory and TMEM go away
   tc::fenceBeforeThreadSync();
-  __syncthreads();
-  if (warp == 1) tc::tmemDealloc(tmemBase, kTmemCols);
+  if constexpr (CTAS == 2) tc::clusterSync(); else __syncthreads();   // neither CTA frees TMEM the pair's MMA still writes
+  if (warp == 1) {
+    if constexpr (CTAS == 2) tc::tmemDeallocPair(tmemBase, kTmemCols);
+    else tc::tmemDealloc(tmemBase, kTmemCols);
+  }
   if constexpr (COMM != kCommNone) {
     if (threadIdx.x == 0) {
       __threadfence();
@@ -441,32 +502,58 @@ int chooseBn(int M, int N, int epilogue) {
   return best;
 }
 
-bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn) {
+// a CTA pair per 256-row block when the rows allow it (and PURLIN_GEMM_SINGLE_CTA is not set)
+int ctasFor(int M, int rowsPerRank) {
+  static const bool single = std::getenv("PURLIN_GEMM_SINGLE_CTA") != nullptr;
+  if (single) return 1;
+  return (rowsPerRank % (2 * kBM) == 0 && M >= 2 * kBM) ? 2 : 1;
+}
+
+bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas) {
   if (M <= 0 || N <= 0 || K <= 0) { setError("GEMM dimensions must be positive"); return false; }
   if (K % 8 || N % 8) { setError("N and K must be multiples of 8"); return false; }
   if (bn == 0) bn = chooseBn(M, N, epilogue);
   if (bn % 16 || bn < 16 || bn > kMaxBN || (epilogue == kEpiSwiglu && bn % 32)) { setError("tile width must be a multiple of 16 (32 for SwiGLU) up to 256"); return false; }
   p.M = M; p.N = N; p.K = K; p.bn = bn;
-  p.tilesM = (M + kBM - 1) / kBM; p.tilesN = (N + bn - 1) / bn;
-  const int stageBytes = kABytes + bn * kBK * 2;
+  if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
+  p.tilesM = (M + kBM * ctas - 1) / (kBM * ctas); p.tilesN = (N + bn - 1) / bn;
+  const int stageBytes = kABytes + (bn / ctas) * kBK * 2;
   p.stages = std::min((kSmemBudget - kBarrierBytes - 1024) / stageBytes, kMaxStages);
   return true;
 }
-size_t smemFor(const Params& p) { return size_t(p.stages) * (kABytes + p.bn * kBK * 2) + kBarrierBytes + 1024; }
+size_t smemFor(const Params& p, int ctas) { return size_t(p.stages) * (kABytes + (p.bn / ctas) * kBK * 2) + kBarrierBytes + 1024; }
 
-template <int EPI, int COMM>
-int launch(const Maps& maps, const Params& p, cudaStream_t stream) {
-  auto kernel = gemmKernel<EPI, COMM>;
-  static bool optedIn = false;
-  if (!optedIn) {
+template <int EPI, int COMM, int CTAS>
+int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
+  auto kernel = gemmKernel<EPI, COMM, CTAS>;
+  constexpr int threads = COMM == kCommAG ? kThreadsComm : kThreadsPlain;
+  static int maxClusters = -1;
+  if (maxClusters < 0) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) { setError("cannot opt in to 227 KiB of shared memory"); return 1; }
-    optedIn = true;
+    maxClusters = smCount() / CTAS;
+    if (CTAS == 2) {
+      // pairs must sit on SMs of one GPC: ask how many pairs the device can hold at once
+      cudaLaunchConfig_t q{};
+      cudaLaunchAttribute qa[1];
+      qa[0].id = cudaLaunchAttributeClusterDimension; qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
+      q.gridDim = dim3(smCount() / 2 * 2); q.blockDim = dim3(threads); q.dynamicSmemBytes = kSmemBudget; q.attrs = qa; q.numAttrs = 1;
+      int n = 0;
+      if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) == cudaSuccess && n > 0) maxClusters = std::min(maxClusters, n);
+    }
   }
-  const int grid = std::min(p.tilesM * p.tilesN, smCount());
-  kernel<<<grid, COMM == kCommAG ? kThreadsComm : kThreadsPlain, smemFor(p), stream>>>(maps, p);
-  const cudaError_t e = cudaGetLastError();
+  const int pairs = std::min(p.tilesM * p.tilesN, maxClusters);
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(pairs * CTAS); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smemFor(p, CTAS); cfg.stream = stream;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps, p);
   if (e != cudaSuccess) { setError(std::string("GEMM launch: ") + cudaGetErrorString(e)); return 1; }
   return 0;
+}
+template <int EPI, int COMM>
+int launch(const Maps& maps, const Params& p, int ctas, cudaStream_t stream) {
+  return ctas == 2 ? launchImpl<EPI, COMM, 2>(maps, p, stream) : launchImpl<EPI, COMM, 1>(maps, p, stream);
 }
 
 }  // namespace
@@ -504,10 +591,11 @@ extern "C" {
 
 int purlin_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int bn, uint32_t* status, void* stream) {
   Params p{};
-  if (!fillShape(p, M, N, K, epilogue, bn)) return 1;
+  const int ctas = ctasFor(M, M);
+  if (!fillShape(p, M, N, K, epilogue, bn, ctas)) return 1;
   Maps maps{};
   if (!makeMap(&maps.a, A, uint64_t(M), uint64_t(K), kBM)) return 1;
-  if (!makeMap(&maps.b, B, uint64_t(N), uint64_t(K), uint32_t(p.bn))) return 1;
+  if (!makeMap(&maps.b, B, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
   maps.aLocal = maps.a;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.ldc = epilogue == kEpiSwiglu ? N / 2 : N;
@@ -515,7 +603,7 @@ int purlin_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K,
   p.timeoutNs = 2ull * 1000 * 1000 * 1000;
   p.rank = 0; p.world = 1; p.blocksPerRank = p.tilesM;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommNone>(maps, p, s) : launch<kEpiStore, kCommNone>(maps, p, s);
+  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommNone>(maps, p, ctas, s) : launch<kEpiStore, kCommNone>(maps, p, ctas, s);
 }
 
 size_t purlin_tp_workspace_bytes(int world, int M, int kAg, int nRs) { return tpLayout(world, M, kAg, nRs).total; }
@@ -560,9 +648,10 @@ int purlin_tp_clear_status(PurlinTpContext* c, void* stream) {
 int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, void* out, int M, int N, int K, int epilogue, void* stream) {
   if (M > c->M || K > c->kAg || M % (c->world * kBM)) { setError("all-gather GEMM shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
-  if (!fillShape(p, M, N, K, epilogue, 0)) return 1;
+  const int ctas = ctasFor(M, M / c->world);
+  if (!fillShape(p, M, N, K, epilogue, 0, ctas)) return 1;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
-  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / kBM;
+  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * ctas);
   p.epoch = reinterpret_cast<uint64_t*>(lb); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
   p.status = reinterpret_cast<uint32_t*>(lb + 256); p.timeoutNs = c->timeoutNs;
   p.pushCounters = reinterpret_cast<uint32_t*>(lb + 4096);
@@ -575,21 +664,22 @@ int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, voi
   if (!makeMap(&maps.a1, c->peers[c->rank] + c->gatherOff[1], uint64_t(M), uint64_t(K), kBM)) return 1;
   p.gatherParityBytes = c->gatherOff[1] - c->gatherOff[0];
   if (!makeMap(&maps.aLocal, xLocal, uint64_t(M / c->world), uint64_t(K), kBM)) return 1;
-  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn))) return 1;
+  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
   for (int q = 0; q < c->world; ++q) {
     p.gatherBuf[q] = reinterpret_cast<__nv_bfloat16*>(c->peers[q] + c->gatherOff[0]);
     p.rowReady[q] = reinterpret_cast<uint64_t*>(c->peers[q] + c->rowReadyOff);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommAG>(maps, p, s) : launch<kEpiStore, kCommAG>(maps, p, s);
+  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommAG>(maps, p, ctas, s) : launch<kEpiStore, kCommAG>(maps, p, ctas, s);
 }
 
 int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* out, int M, int N, int K, void* stream) {
   if (M > c->M || N > c->nRs || M % (c->world * kBM)) { setError("GEMM reduce-scatter shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
-  if (!fillShape(p, M, N, K, kEpiStore, 0)) return 1;
+  const int ctas = ctasFor(M, M / c->world);
+  if (!fillShape(p, M, N, K, kEpiStore, 0, ctas)) return 1;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
-  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / kBM;
+  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * ctas);
   p.epoch = reinterpret_cast<uint64_t*>(lb + 128); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 192);
   p.status = reinterpret_cast<uint32_t*>(lb + 256); p.timeoutNs = c->timeoutNs;
   p.C = static_cast<__nv_bfloat16*>(out); p.ldc = N;
@@ -597,12 +687,12 @@ int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* ou
   Maps maps{};
   if (!makeMap(&maps.a, A, uint64_t(M), uint64_t(K), kBM)) return 1;
   maps.aLocal = maps.a;
-  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn))) return 1;
+  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
   for (int q = 0; q < c->world; ++q) {
     p.partialBuf[q] = reinterpret_cast<__nv_bfloat16*>(c->peers[q] + c->partialOff);
     p.tileReady[q] = reinterpret_cast<uint64_t*>(c->peers[q] + c->tileReadyOff);
   }
-  return launch<kEpiStore, kCommRS>(maps, p, static_cast<cudaStream_t>(stream));
+  return launch<kEpiStore, kCommRS>(maps, p, ctas, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
