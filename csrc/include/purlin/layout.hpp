@@ -24,6 +24,8 @@
 #include "context.hpp"
 #include "plan.hpp"
 
+namespace purlin { namespace bulk { constexpr int kPlanMaxDepth = 13; constexpr size_t kPlanTileBytes = 16384; } }
+
 namespace purlin {
 
 enum class Notify : int32_t { allPeers = 0, one = 1 };
@@ -237,7 +239,9 @@ inline bool buildPlan(const CollectiveSpec& spec, const Policy& pol, const Works
   plan.threads = pol.threads;
   plan.mmDepth = pol.mmDepth;
   plan.unroll = pol.unroll;
-  plan.stageDepth = pol.stageDepth;
+  plan.stageDepth = std::min(std::max(pol.stageDepth, 0), bulk::kPlanMaxDepth);
+  if (plan.stageDepth == 1) plan.stageDepth = 2;   // a ring needs a tile in flight and a tile being stored
+  plan.smemBytes = (plan.stageDepth > 0 && pol.regime == int32_t(Regime::throughput)) ? size_t(plan.stageDepth) * bulk::kPlanTileBytes + 256 : 0;
   const bool ok = pol.regime == int32_t(Regime::latency) ? buildLatencyPlan(spec, pol, ws, plan, err)
                                                           : buildThroughputPlan(spec, pol, ws, plan, err);
   if (!ok) return false;

@@ -14,6 +14,7 @@
 // global memory); every wait is bounded.
 #pragma once
 #include "atom.cuh"
+#include "bulk.cuh"
 #include "packet.cuh"
 #include "plan.hpp"
 
@@ -37,6 +38,8 @@ struct Frame {
   unsigned char* dst;
   int unroll;
   int mmDepth;
+  int bulkDepth;            // > 0: copy roles stream through the bulk-async ring in `smem`
+  unsigned char* smem;
 };
 
 PURLIN_D size_t chunkLen(const Step& s, uint32_t k) {
@@ -60,10 +63,79 @@ PURLIN_D bool ctaWaitAll(const Context& ctx, uint64_t* const* table, int slot, u
   return __syncthreads_and(ok) != 0;
 }
 
+// ---------------- copy roles on the bulk-async engine (one driver thread per CTA) ----------------
+struct StageHooks {
+  const Context& ctx; const Step& s; int si; const Frame& f; unsigned char* staging; int n;
+  PURLIN_D const unsigned char* src(uint32_t k, size_t off) const { return f.src + s.srcOff + size_t(k) * s.chunkBytes + off; }
+  PURLIN_D unsigned char* dst(uint32_t k, size_t off) const { return staging + slotOff(s, k) + off; }
+  PURLIN_D bool beforeLoad(uint32_t) const { return true; }
+  PURLIN_D void loaded(uint32_t) const {}
+  PURLIN_D bool beforeStore(uint32_t k) const {
+    if (!(s.flags & kFlagCyclic) || k < s.slots) return true;
+    const uint64_t need = flagValue(f.seq, k - s.slots);      // every reader drained the slot's previous tenant
+    if (s.peer >= 0) return sig::waitAtLeast(ctx, ctx.consumedSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k);
+    for (int q = 0; q < ctx.world; ++q) {
+      if (q == ctx.rank && !(s.flags & kFlagDrainSelf)) continue;
+      if (!sig::waitAtLeast(ctx, ctx.consumedSignals[ctx.rank] + q, need, kStatusTimeoutSignal, si, q, k)) return false;
+    }
+    return true;
+  }
+  PURLIN_D void stored(uint32_t k) const {
+    tc::fenceProxyAsync();                                    // bulk (async-proxy) writes before the generic-proxy flag
+    if (sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
+      const uint64_t v = flagValue(f.seq, k);
+      if (s.peer >= 0) sig::stReleaseSys(ctx.signals[s.peer] + ctx.rank, v);
+      else for (int q = 0; q < ctx.world; ++q) sig::stReleaseSys(ctx.signals[(ctx.rank + q) % ctx.world] + ctx.rank, v);
+    }
+  }
+};
+
+struct ConsumeHooks {
+  const Context& ctx; const Step& s; int si; const Frame& f; const unsigned char* staging; const uint64_t* flag; int n;
+  PURLIN_D const unsigned char* src(uint32_t k, size_t off) const { return staging + slotOff(s, k) + off; }
+  PURLIN_D unsigned char* dst(uint32_t k, size_t off) const { return f.dst + s.dstOff + size_t(k) * s.chunkBytes + off; }
+  PURLIN_D bool beforeLoad(uint32_t k) const {
+    if (!sig::waitAtLeast(ctx, flag, flagValue(f.seq, k), kStatusTimeoutSignal, si, s.peer, k)) return false;
+    tc::fenceProxyAsync();                                    // the producer's writes before this thread's bulk reads
+    return true;
+  }
+  PURLIN_D void loaded(uint32_t k) const {
+    if ((s.flags & kFlagCyclic) && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n))
+      sig::stReleaseSys(ctx.consumedSignals[s.peer] + ctx.rank, flagValue(f.seq, k));
+  }
+  PURLIN_D bool beforeStore(uint32_t) const { return true; }
+  PURLIN_D void stored(uint32_t) const {}
+};
+
+struct LocalHooks {
+  const Step& s; const Frame& f;
+  PURLIN_D const unsigned char* src(uint32_t, size_t off) const { return f.src + s.srcOff + off; }
+  PURLIN_D unsigned char* dst(uint32_t, size_t off) const { return f.dst + s.dstOff + off; }
+  PURLIN_D bool beforeLoad(uint32_t) const { return true; }
+  PURLIN_D void loaded(uint32_t) const {}
+  PURLIN_D bool beforeStore(uint32_t) const { return true; }
+  PURLIN_D void stored(uint32_t) const {}
+};
+
+template <class Hooks>
+PURLIN_D bool runBulk(const Context& ctx, const Step& s, const Frame& f, Hooks& h) {
+  int ok = 1;
+  if (threadIdx.x == 0) {
+    bulk::Ring ring;
+    ring.init(f.smem, f.bulkDepth, ctx.timeoutNs);
+    // a reader of a cyclic window may not run further ahead than the window has slots
+    const uint32_t lead = ((s.flags & kFlagCyclic) && s.role != kRoleStage) ? (s.slots > 1 ? s.slots - 1 : 0u) : 0x3fffffffu;
+    ok = bulk::stream(ring, s, f.bIdx - s.blockBegin, s.blockCount, lead, h) ? 1 : 0;
+    if (!ok && !sig::failed(ctx)) sig::fail(ctx, kStatusTimeoutBarrier, 0, uint32_t(s.peer), 0);
+  }
+  return __syncthreads_and(ok) != 0;
+}
+
 template <class Atom>
 PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
   const int j = f.bIdx - s.blockBegin, n = s.blockCount;
   unsigned char* staging = ctx.stagingTR[ctx.rank] + size_t(f.half) * ctx.stagingTRSize + s.dstOff;
+  if (f.bulkDepth > 0) { StageHooks h{ctx, s, si, f, staging, n}; return runBulk(ctx, s, f, h); }
   for (uint32_t k = 0; k < s.chunks; ++k) {
     if ((s.flags & kFlagCyclic) && k >= s.slots) {
       // back-pressure: every reader of this slot must have drained its previous tenant
@@ -85,7 +157,8 @@ PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
 }
 
 template <class Atom>
-PURLIN_D void local(const Step& s, const Frame& f) {
+PURLIN_D void local(const Context& ctx, const Step& s, const Frame& f) {
+  if (f.bulkDepth > 0) { LocalHooks h{s, f}; runBulk(ctx, s, f, h); return; }
   superCopy<Atom>(f.dst + s.dstOff, f.src + s.srcOff, s.bytes, f.bIdx - s.blockBegin, s.blockCount, f.unroll);
 }
 
@@ -96,6 +169,7 @@ PURLIN_D bool consume(const Context& ctx, const Step& s, int si, const Frame& f,
   const int from = (s.flags & kFlagLocalSource) ? ctx.rank : s.peer;
   const unsigned char* staging = ctx.stagingTR[from] + size_t(f.half) * ctx.stagingTRSize + s.srcOff;
   uint64_t* const* table = gather ? ctx.gatherSignals : ctx.signals;
+  if (f.bulkDepth > 0) { ConsumeHooks h{ctx, s, si, f, staging, table[ctx.rank] + s.peer, n}; return runBulk(ctx, s, f, h); }
   for (uint32_t k = 0; k < s.chunks; ++k) {
     if (!ctaWait(ctx, table[ctx.rank] + s.peer, flagValue(f.seq, k), kStatusTimeoutSignal, si, s.peer, k)) return false;
     superCopy<Atom>(f.dst + s.dstOff + size_t(k) * s.chunkBytes, staging + slotOff(s, k), chunkLen(s, k), j, n, f.unroll);
@@ -107,6 +181,7 @@ PURLIN_D bool consume(const Context& ctx, const Step& s, int si, const Frame& f,
   }
   return true;
 }
+
 
 template <class Atom, DType T, ReduceOp Op>
 PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, const unsigned char** peerPtr) {
@@ -249,7 +324,7 @@ PURLIN_D bool awaitArrival(const Context& ctx, const Frame& f) {
 // grid size of this rank (not of the launch: emulation stacks ranks along grid.y).
 template <class Atom, DType T, ReduceOp Op, bool Reduces>
 PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src, unsigned char* dst,
-                  int bIdx, int blocks, const unsigned char** peerPtr) {
+                  int bIdx, int blocks, const unsigned char** peerPtr, unsigned char* dynSmem) {
   Frame f;
   f.seq = sig::ldRelaxedSys(ctx.seq);
   f.half = int(f.seq & 1);
@@ -258,6 +333,8 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
   f.dst = dst;
   f.unroll = plan.unroll;
   f.mmDepth = plan.mmDepth;
+  f.bulkDepth = plan.regime == int32_t(Regime::throughput) ? plan.stageDepth : 0;
+  f.smem = dynSmem;
   bool ok = !sig::failed(ctx);    // a context that failed stays quiet until the host clears it
   if (ok && plan.varLenArrival && bIdx == 0) postArrival(ctx, f, plan.payloadBytes);
   for (int si = 0; si < plan.nSteps && ok; ++si) {
@@ -265,7 +342,7 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
     if (bIdx < s.blockBegin || bIdx >= s.blockBegin + s.blockCount) continue;
     switch (s.role) {
       case kRoleStage: ok = stage<Atom>(ctx, s, si, f); break;
-      case kRoleLocal: local<Atom>(s, f); break;
+      case kRoleLocal: local<Atom>(ctx, s, f); break;
       case kRoleConsume: ok = consume<Atom>(ctx, s, si, f, false); break;
       case kRoleGather: ok = consume<Atom>(ctx, s, si, f, true); break;
       case kRolePacketPut: packetPut(ctx, s, f); break;

@@ -58,7 +58,8 @@ template <DType T, ReduceOp Op, bool Reduces>
 __global__ void __launch_bounds__(kMaxThreads, 1)
 snacKernel(const __grid_constant__ Context ctx, const __grid_constant__ Plan plan, const unsigned char* src, unsigned char* dst) {
   __shared__ const unsigned char* peerPtr[kMaxRanks];
-  snac::run<Atom, T, Op, Reduces>(ctx, plan, src, dst, blockIdx.x, gridDim.x, peerPtr);
+  extern __shared__ __align__(128) unsigned char dynSmem[];
+  snac::run<Atom, T, Op, Reduces>(ctx, plan, src, dst, blockIdx.x, gridDim.x, peerPtr, dynSmem);
 }
 
 // Emulation launch: grid.y virtual ranks on one GPU (cooperative, so all CTAs are resident
@@ -85,7 +86,8 @@ __global__ void __launch_bounds__(kMaxThreads, 1) snacEmuKernel(const EmuRank* r
   const Context& ctx = *reinterpret_cast<const Context*>(ctxMem);
   const Plan& plan = *reinterpret_cast<const Plan*>(planMem);
   if (int(blockIdx.x) >= plan.blocks) return;
-  snac::run<Atom, T, Op, Reduces>(ctx, plan, me.src, me.dst, blockIdx.x, plan.blocks, peerPtr);
+  extern __shared__ __align__(128) unsigned char dynSmem[];
+  snac::run<Atom, T, Op, Reduces>(ctx, plan, me.src, me.dst, blockIdx.x, plan.blocks, peerPtr, dynSmem);
 }
 
 template <class Atom_>
@@ -157,10 +159,22 @@ int worldOneCopy(const CollectiveSpec& s, const void* src, void* dst, cudaStream
   return 0;
 }
 
+// kernels that stream through the bulk ring need more dynamic shared memory than the default limit: opt in once each
+bool ensureSmemOptIn(const void* fn) {
+  static std::mutex mu;
+  static std::vector<const void*> done;
+  std::lock_guard<std::mutex> g(mu);
+  for (const void* f : done) if (f == fn) return true;
+  if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bulk::smemBytes(bulk::kMaxDepth))) != cudaSuccess) return false;
+  done.push_back(fn);
+  return true;
+}
+
 int launchPlan(PurlinHostContext* h, const Plan& plan, const void* src, void* dst, cudaStream_t stream) {
   ProdFn fn = prodKernel(plan);
   const int threads = std::min(std::max(plan.threads, 32), kMaxThreads);
-  fn<<<plan.blocks, threads, 0, stream>>>(h->dev, plan, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst));
+  if (plan.smemBytes > 0 && !ensureSmemOptIn(reinterpret_cast<const void*>(fn))) { setError("cannot opt in to the bulk ring's shared memory"); return 1; }
+  fn<<<plan.blocks, threads, plan.smemBytes, stream>>>(h->dev, plan, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst));
   CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -351,17 +365,20 @@ int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collect
   }
   threads = std::min(threads, kMaxThreads);
   EmuFn fn = emuKernel(host[0].plan);
+  size_t dyn = 0;
+  for (int r = 0; r < world; ++r) dyn = std::max<size_t>(dyn, host[r].plan.smemBytes);
+  if (dyn > 0 && !ensureSmemOptIn(reinterpret_cast<const void*>(fn))) { setError("cannot opt in to the bulk ring's shared memory"); return 1; }
   int perSm = 0, dev = 0, sms = 0;
   CUDA_OK(cudaGetDevice(&dev));
   CUDA_OK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
-  CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, threads, 0));
+  CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSm, fn, threads, dyn));
   if (blocks * world > perSm * sms) { setError("emulated grid does not fit on the GPU at once; use fewer CTAs per rank"); return 1; }
   EmuRank* devRanks = nullptr;
   CUDA_OK(cudaMallocAsync(&devRanks, sizeof(EmuRank) * world, s));
   CUDA_OK(cudaMemcpyAsync(devRanks, host.data(), sizeof(EmuRank) * world, cudaMemcpyHostToDevice, s));
   CUDA_OK(cudaStreamSynchronize(s));   // `host` is pageable and dies with this frame
   void* args[] = {&devRanks};
-  CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fn), dim3(blocks, world), dim3(threads), args, 0, s));
+  CUDA_OK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(fn), dim3(blocks, world), dim3(threads), args, dyn, s));
   CUDA_OK(cudaFreeAsync(devRanks, s));
   return 0;
 }

@@ -146,6 +146,8 @@ def initialize(group=None, device: Optional[torch.device] = None, arch: int = 10
     ctx = mod.purlin_context_create(rank, world, ptrs, int(mc_ptr or 0), staging_size, timeout_ns, stream)
     if not ctx:
         raise RuntimeError("purlin: " + _native.last_error(mod))
+    from . import tuning
+    tuning.load_for(torch.cuda.get_device_name(device), world, lib=mod)   # measured codesign table, if one exists
     return ContextHandle(mod, ctx, buf, hdl, rank, world, device, group, staging_size, layout)
 
 

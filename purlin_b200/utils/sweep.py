@@ -51,27 +51,29 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
                 if multicast:
                     out.append(("lr2-mc", _policy(regime=0, arPath=1, lrBlocks=b, lrMulticast=1)))
         if nbytes >= 64 << 10:
-            chunks = [0] if nbytes <= 2 << 20 else [c for c in (512 << 10, 2 << 20, 8 << 20) if c < nbytes]
+            chunks = [0] if nbytes <= 2 << 20 else [c for c in (2 << 20, 8 << 20, 32 << 20) if c < nbytes]
             for c in chunks:
-                for put, con, gat in ((16, 32, 16), (32, 48, 32), (32, 64, 48)):
-                    if world == 2:
-                        out.append(("tr-direct", _policy(arPath=0, putBlocks=put, consumeBlocks=con + gat, chunkBytes=c)))
-                    out.append(("tr-2shot", _policy(arPath=1, putBlocks=put, consumeBlocks=con, gatherBlocks=gat, chunkBytes=c)))
-                if multicast:
-                    for con, depth in ((16, 4), (32, 4), (32, 8), (64, 4)):
-                        out.append(("nvls", _policy(arPath=1, memType=1, putBlocks=32, consumeBlocks=con, gatherBlocks=32, mmDepth=depth, chunkBytes=c)))
+                for ring in (0,):
+                    for put, con, gat in ((16, 32, 16), (32, 64, 32), (24, 96, 24), (32, 80, 32)):
+                        if world == 2:
+                            out.append((f"tr-direct-r{ring}", _policy(arPath=0, putBlocks=put, consumeBlocks=con + gat, chunkBytes=c, stageDepth=ring)))
+                        out.append((f"tr-2shot-r{ring}", _policy(arPath=1, putBlocks=put, consumeBlocks=con, gatherBlocks=gat, chunkBytes=c, stageDepth=ring)))
+                    if multicast:
+                        for put, con, gat, depth in ((16, 32, 16, 4), (32, 64, 32, 8), (24, 96, 24, 8), (32, 32, 32, 8), (48, 48, 48, 8), (40, 64, 40, 4)):
+                            out.append((f"nvls-r{ring}", _policy(arPath=1, memType=1, putBlocks=put, consumeBlocks=con, gatherBlocks=gat, mmDepth=depth, chunkBytes=c, stageDepth=ring)))
     else:
         per_rank_total = nbytes * world
         if nbytes <= slot:
             for b in lr_blocks:
                 out.append(("lr", _policy(regime=0, lrBlocks=b)))
         if per_rank_total >= 64 << 10:
-            chunks = [0] if nbytes <= 1 << 20 else [c for c in (512 << 10, 2 << 20, 4 << 20) if c < nbytes]
+            chunks = [0] if nbytes <= 1 << 20 else [c for c in (1 << 20, 4 << 20, 16 << 20) if c < nbytes]
             for c in chunks:
-                for put, con in ((16, 32), (32, 64), (32, 96)):
-                    out.append(("tr", _policy(putBlocks=max(put, world), consumeBlocks=con, chunkBytes=c)))
-                if coll == "rs" and multicast:
-                    out.append(("nvls", _policy(memType=1, putBlocks=32, consumeBlocks=32, chunkBytes=c)))
+                for ring in (0,):
+                    for put, con in ((16, 32), (32, 64), (32, 96), (24, 112)):
+                        out.append((f"tr-r{ring}", _policy(putBlocks=max(put, world), consumeBlocks=con, chunkBytes=c, stageDepth=ring)))
+                    if coll == "rs" and multicast:
+                        out.append((f"nvls-r{ring}", _policy(memType=1, putBlocks=32, consumeBlocks=64, mmDepth=8, chunkBytes=c, stageDepth=ring)))
     return out
 
 
@@ -96,6 +98,8 @@ def main():
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world, device_id=dev)
+    if args.tune:
+        os.environ["PURLIN_NO_TUNING_TABLE"] = "1"   # candidates are forced; the built-in policy is the fallback
     h = purlin.initialize(dist.group.WORLD, dev, 100, None)
     td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
     esz = torch.empty(0, dtype=td).element_size()
@@ -182,7 +186,7 @@ def main():
                             print(f"# skipped {coll} {n} {label}: {e}", flush=True)
                         continue
                     if rank == 0:
-                        print("# " + bench.csv_row(coll, f"cand:{label}:{pol.putBlocks}/{pol.consumeBlocks}/{pol.gatherBlocks}/{pol.lrBlocks}/c{pol.chunkBytes}/d{pol.mmDepth}", world, total, args.dtype, t), flush=True)
+                        print("# " + bench.csv_row(coll, f"cand:{label}:{pol.putBlocks}/{pol.consumeBlocks}/{pol.gatherBlocks}/{pol.lrBlocks}/c{pol.chunkBytes >> 10}K/d{pol.mmDepth}", world, total, args.dtype, t), flush=True)
                     if best is None or t.us < best[0].us:
                         best = (t, label, pol)
                 if best is not None:
@@ -201,10 +205,11 @@ def main():
                     print(bench.csv_row(coll, "nccl", world, total, args.dtype, t), flush=True)
             n *= args.factor
     if args.tune and rank == 0:
-        path = args.table_out or os.path.join("gpurun_out", f"tuning_w{world}.json")
+        from purlin_b200 import tuning
+        path = args.table_out or os.path.join("gpurun_out", str(tuning.table_path(torch.cuda.get_device_name(), world).name))
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         with open(path, "w") as f:
-            json.dump({"gpu": torch.cuda.get_device_name(), "world": world, "entries": table}, f, indent=1)
+            json.dump({"gpu": torch.cuda.get_device_name(), "world": world, "dtype": args.dtype, "entries": table}, f, indent=1, sort_keys=True)
         print(f"# wrote {path}", flush=True)
     purlin.finalize(h)
     dist.destroy_process_group()

@@ -141,3 +141,26 @@ def test_absent_rank_times_out_and_context_recovers():
     ew = EmulatedWorld(4, 1 << 20, timeout_ms=2000)
     run_case(ew, AR, nbytes=16384, dtype=4, pol=policy(arPath=1))
     ew.close()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("depth", [2, 5, 13])
+def test_bulk_async_engine(worlds, world, depth):
+    # the copy roles stream through the cp.async.bulk ring: uneven tails, chunk boundaries inside and across tiles,
+    # CTAs with no bytes in a chunk, cyclic slots, composed all-reduce (stage and gather on the ring, reduce in registers)
+    for coll, n, kw in ((AG, 98304 + 64, dict()), (AG, 200000 // 32 * 32, dict(chunkBytes=32768)), (A2A, 65536 + 32, dict(chunkBytes=16384)),
+                        (RS, 65536, dict(chunkBytes=8192)), (AR, world * 32 * 771, dict(arPath=1)),
+                        (AR, world * 32 * 771, dict(arPath=1, chunkBytes=world * 4096)), (AR, 1 << 17, dict(arPath=0, chunkBytes=16384))):
+        run_case(worlds(world), coll, nbytes=n, dtype=4, pol=policy(stageDepth=depth, **kw))
+    sizes = _sizes(world, 5, scale=131072, zero_every=3)
+    for coll in (AGV, RSV):
+        run_case(worlds(world), coll, sizes=sizes, dtype=0, pol=policy(stageDepth=depth, chunkBytes=16384), seed=5)
+    mat = [_sizes(world, 40 + r, scale=65536, zero_every=4) for r in range(world)]
+    run_case(worlds(world), A2AV, sizes=mat, dtype=0, pol=policy(stageDepth=depth, perStreamThreshold=4096, chunkBytes=16384), seed=6)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_bulk_async_engine_cyclic(worlds, world):
+    st = 256 << 10
+    for coll, n in ((AG, 1 << 20), (RS, 1 << 19), (A2A, 1 << 19), (AR, 1 << 20)):
+        run_case(worlds(world, st), coll, nbytes=n, dtype=4, pol=policy(chunkBytes=32768, arPath=0, stageDepth=6))
