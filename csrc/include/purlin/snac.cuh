@@ -63,6 +63,18 @@ PURLIN_D bool ctaWaitAll(const Context& ctx, uint64_t* const* table, int slot, u
   return __syncthreads_and(ok) != 0;
 }
 
+// Thread 0 takes part in the last-arrival count; every thread of the CTA learns whether this CTA was last.
+// The two barriers also order every thread's earlier writes before any thread's later flag store, so each
+// peer can be signalled by a different thread (a release store to peer memory costs microseconds; W of them
+// issued by one thread in sequence would dominate a chunk).
+PURLIN_D bool ctaLastArrival(uint32_t* counter, uint32_t expected) {
+  __shared__ int lastFlag;
+  __syncthreads();
+  if (threadIdx.x == 0) lastFlag = sig::lastArrival(counter, expected) ? 1 : 0;
+  __syncthreads();
+  return lastFlag != 0;
+}
+
 // ---------------- copy roles on the bulk-async engine (one driver thread per CTA) ----------------
 struct StageHooks {
   const Context& ctx; const Step& s; int si; const Frame& f; unsigned char* staging; int n;
@@ -85,7 +97,10 @@ struct StageHooks {
     if (sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
       const uint64_t v = flagValue(f.seq, k);
       if (s.peer >= 0) sig::stReleaseSys(ctx.signals[s.peer] + ctx.rank, v);
-      else for (int q = 0; q < ctx.world; ++q) sig::stReleaseSys(ctx.signals[(ctx.rank + q) % ctx.world] + ctx.rank, v);
+      else {
+        __threadfence_system();                               // one fence, then relaxed flag stores to every rank
+        for (int q = 0; q < ctx.world; ++q) sig::stRelaxedSys(ctx.signals[(ctx.rank + q) % ctx.world] + ctx.rank, v);
+      }
     }
   }
 };
@@ -146,11 +161,10 @@ PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
       if (!ok) return false;
     }
     superCopy<Atom>(staging + slotOff(s, k), f.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), j, n, f.unroll);
-    __syncthreads();
-    if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
+    if (ctaLastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
       const uint64_t v = flagValue(f.seq, k);
-      if (s.peer >= 0) sig::stReleaseSys(ctx.signals[s.peer] + ctx.rank, v);
-      else for (int q = 0; q < ctx.world; ++q) sig::stReleaseSys(ctx.signals[(ctx.rank + q) % ctx.world] + ctx.rank, v);
+      if (s.peer >= 0) { if (threadIdx.x == 0) sig::stReleaseSys(ctx.signals[s.peer] + ctx.rank, v); }
+      else if (int(threadIdx.x) < ctx.world) sig::stReleaseSys(ctx.signals[(ctx.rank + threadIdx.x) % ctx.world] + ctx.rank, v);
     }
   }
   return true;
@@ -208,14 +222,11 @@ PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, 
     if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth);
     if (s.flags & (kFlagNotifyGather | kFlagCyclic)) {
       if (s.flags & kFlagMulticastOut) __threadfence_system();
-      __syncthreads();
-      if (threadIdx.x == 0 && sig::lastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n)) {
+      if (ctaLastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n) && int(threadIdx.x) < ctx.world) {
         const uint64_t v = flagValue(f.seq, k);
-        for (int q = 1; q <= ctx.world; ++q) {
-          const int p = (ctx.rank + q) % ctx.world;
-          if ((s.flags & kFlagNotifyGather) && p != ctx.rank) sig::stReleaseSys(ctx.gatherSignals[p] + ctx.rank, v);
-          if (s.flags & kFlagCyclic) sig::stReleaseSys(ctx.consumedSignals[p] + ctx.rank, v);
-        }
+        const int p = (ctx.rank + 1 + threadIdx.x) % ctx.world;     // one peer per thread
+        if ((s.flags & kFlagNotifyGather) && p != ctx.rank) sig::stReleaseSys(ctx.gatherSignals[p] + ctx.rank, v);
+        if (s.flags & kFlagCyclic) sig::stReleaseSys(ctx.consumedSignals[p] + ctx.rank, v);
       }
     } else {
       __syncthreads();   // peerPtr is rewritten by the next chunk

@@ -203,11 +203,11 @@ __global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_const
     }
   }
   // 5. all of this rank's rows are on their way: the last CTA tells every destination
+  __shared__ int lastCta;
   __syncthreads();
-  if (tid == 0) {
-    if (sig::lastArrival(p.pushCounters, gridDim.x))
-      for (int q = 0; q < p.world; ++q) sig::stReleaseSys(p.flags[(p.rank + q) % p.world] + p.world + p.rank, epoch);
-  }
+  if (tid == 0) lastCta = sig::lastArrival(p.pushCounters, gridDim.x) ? 1 : 0;
+  __syncthreads();
+  if (lastCta && tid < p.world) sig::stReleaseSys(p.flags[(p.rank + tid) % p.world] + p.world + p.rank, epoch);   // one peer per thread
   // 6. this rank's receive buffer is complete when every sender has said so
   if (blockIdx.x == 0 && ok) waitAllRanks(p, p.world, epoch, 3);
   __syncthreads();
@@ -269,9 +269,11 @@ __global__ void __launch_bounds__(kThreads, 1) combineKernel(const __grid_consta
   }
   // done reading everyone's outputs: the last CTA says so, then the call waits until every rank is done
   // reading this rank's buffers, so the next layer may overwrite them
+  __shared__ int lastCta;
   __syncthreads();
-  if (tid == 0 && sig::lastArrival(p.pushCounters + 1, gridDim.x))
-    for (int q = 0; q < p.world; ++q) sig::stReleaseSys(p.flags[(p.rank + q) % p.world] + 3 * p.world + p.rank, epoch);
+  if (tid == 0) lastCta = sig::lastArrival(p.pushCounters + 1, gridDim.x) ? 1 : 0;
+  __syncthreads();
+  if (lastCta && tid < p.world) sig::stReleaseSys(p.flags[(p.rank + tid) % p.world] + 3 * p.world + p.rank, epoch);
   if (blockIdx.x == 0 && ok) waitAllRanks(p, 3 * p.world, epoch, 5);
   __syncthreads();
   if (tid == 0) {

@@ -51,7 +51,7 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
                 if multicast:
                     out.append(("lr2-mc", _policy(regime=0, arPath=1, lrBlocks=b, lrMulticast=1)))
         if nbytes >= 64 << 10:
-            chunks = [0] if nbytes <= 2 << 20 else [c for c in (2 << 20, 8 << 20, 32 << 20) if c < nbytes]
+            chunks = [0] if nbytes <= 2 << 20 else [c for c in (1 << 20, 2 << 20, 8 << 20, 32 << 20) if c < nbytes and nbytes // c <= 64] + ([0] if nbytes <= 16 << 20 else [])
             for c in chunks:
                 for ring in (0,):
                     for put, con, gat in ((16, 32, 16), (32, 64, 32), (24, 96, 24), (32, 80, 32)):
@@ -67,7 +67,7 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
             for b in lr_blocks:
                 out.append(("lr", _policy(regime=0, lrBlocks=b)))
         if per_rank_total >= 64 << 10:
-            chunks = [0] if nbytes <= 1 << 20 else [c for c in (1 << 20, 4 << 20, 16 << 20) if c < nbytes]
+            chunks = [0] if nbytes <= 1 << 20 else [c for c in (256 << 10, 1 << 20, 4 << 20, 16 << 20) if c < nbytes and nbytes // c <= 64] + ([0] if nbytes <= 8 << 20 else [])
             for c in chunks:
                 for ring in (0,):
                     for put, con in ((16, 32), (32, 64), (32, 96), (24, 112)):
