@@ -60,7 +60,7 @@ def cache_key(lib: str, sources, flags) -> str:
     h.update(ARCH.encode())
     h.update(" ".join(flags).encode())
     for p in sorted(str(s) for s in list(sources) + _headers()):
-        h.update(p.encode())
+        h.update(Path(p).name.encode())   # contents decide, not where the tree is checked out
         h.update(Path(p).read_bytes())
     return h.hexdigest()[:16]
 
@@ -160,8 +160,27 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
         flags, force, verbose)
 
 
+def build_cpp_tests(force: bool = False, verbose: bool = False):
+    """The C++ host-API test binary (csrc/tests), linked against the in-tree libpurlin_cuda.so."""
+    lib = build_cuda(force, verbose)
+    out = []
+    for src in sorted((CSRC / "tests").glob("*.cu")):
+        exe = LIB_DIR / src.stem
+        stamp = LIB_DIR / (src.stem + ".key")
+        key = cache_key(src.stem, [src, lib], NVCC_FLAGS)
+        if force or not exe.exists() or not stamp.exists() or stamp.read_text().strip() != key:
+            with BuildLock(LIB_DIR / ".build.lock"):
+                tmp = LIB_DIR / f".{src.stem}.{os.getpid()}.tmp"
+                _run([_nvcc(), *NVCC_FLAGS, "-I", str(CSRC / "include"), str(src), "-o", str(tmp), "-L", str(LIB_DIR),
+                      "-lpurlin_cuda", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"], verbose)
+                tmp.replace(exe)
+                stamp.write_text(key)
+        out.append(exe)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return build_host(force, verbose), build_cuda(force, verbose)
+    return build_host(force, verbose), build_cuda(force, verbose), *build_cpp_tests(force, verbose)
 
 
 if __name__ == "__main__":

@@ -70,6 +70,18 @@ _host = None
 _cuda = None
 
 
+def _resolve(name: str, builder):
+    """The in-tree library, rebuilt first when its sources changed (content key); a tree without a compiler
+    uses the library it was shipped with."""
+    path = _build.LIB_DIR / name
+    try:
+        return builder(force=bool(os.environ.get("PURLIN_REBUILD")))
+    except Exception:
+        if path.exists():
+            return path
+        raise
+
+
 def _declare_common(lib):
     lib.purlin_last_error.restype = C.c_char_p
     lib.purlin_plan_sizeof.restype = C.c_size_t
@@ -91,9 +103,7 @@ def host():
     """The CPU-only library; built on first use."""
     global _host
     if _host is None:
-        path = _build.LIB_DIR / "libpurlin_host.so"
-        if not path.exists() or os.environ.get("PURLIN_REBUILD"):
-            path = _build.build_host()
+        path = _resolve("libpurlin_host.so", _build.build_host)
         _host = C.CDLL(str(path))
         _declare_common(_host)
     return _host
@@ -103,9 +113,7 @@ def cuda():
     """The full library (CUDA kernels + host half). Raises if it cannot be loaded."""
     global _cuda
     if _cuda is None:
-        path = _build.LIB_DIR / "libpurlin_cuda.so"
-        if not path.exists() or os.environ.get("PURLIN_REBUILD"):
-            path = _build.build_cuda()
+        path = _resolve("libpurlin_cuda.so", _build.build_cuda)
         lib = C.CDLL(str(path))
         _declare_common(lib)
         vp, sz, i, u64 = C.c_void_p, C.c_size_t, C.c_int, C.c_uint64

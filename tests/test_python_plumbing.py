@@ -1,0 +1,132 @@
+"""Python binding surface on the CPU with a recording stand-in for the native library.
+
+Counterpart of tests/test_python_plumbing.py in the reference: wrappers forward exact pointers, byte counts,
+element types, context, stream and reduction mode; initialize asks the provider for the reference's workspace size
+and forwards the multicast pointer; finalize is idempotent; non-contiguous tensors and bad modes are rejected.
+"""
+import ctypes as C
+
+import pytest
+import torch
+
+import purlin_b200 as purlin
+from purlin_b200 import _native
+
+
+class RecordingLib:
+    """Looks like the ctypes library to the wrappers; records every native call."""
+
+    def __init__(self):
+        self.calls = []
+        self.destroyed = 0
+
+    def purlin_collective(self, ctx, coll, src, dst, nbytes, sizes, out_sizes, dtype, op, mode, policy, stream):
+        self.calls.append(dict(ctx=ctx, coll=int(coll), src=src, dst=dst, nbytes=nbytes,
+                               sizes=None if sizes is None else list(sizes), out_sizes=None if out_sizes is None else list(out_sizes),
+                               dtype=int(dtype), op=int(op), mode=int(mode), policy=policy, stream=stream))
+        return 0
+
+    def purlin_context_create(self, rank, world, ptrs, mc, staging, timeout, stream):
+        self.calls.append(dict(create=True, rank=rank, world=world, ptrs=list(ptrs), mc=mc, staging=staging, stream=stream))
+        return 0xC0FFEE
+
+    def purlin_context_destroy(self, ctx, stream):
+        self.destroyed += 1
+        return 0
+
+    def purlin_context_has_multicast(self, ctx):
+        return 1
+
+    def purlin_last_error(self):
+        return b"recorded"
+
+    def purlin_tuning_add(self, *a):
+        return 0
+
+
+def make_handle(world=4, rank=1):
+    lib = RecordingLib()
+    h = purlin.ContextHandle(lib, 0xC0FFEE, object(), object(), rank, world, torch.device("cuda", 0), None, 1 << 20, {})
+    return lib, h
+
+
+def test_wrappers_forward_pointers_bytes_types_and_mode():
+    lib, h = make_handle(world=4)
+    x = torch.zeros(4 * 64, dtype=torch.bfloat16)
+    y = torch.zeros(4 * 64, dtype=torch.bfloat16)
+    purlin.all_reduce(x, y, h, 77, purlin.ReductionMode.DETERMINISTIC)
+    c = lib.calls[-1]
+    assert (c["coll"], c["src"], c["dst"], c["nbytes"], c["dtype"], c["mode"], c["stream"], c["ctx"]) == \
+           (0, x.data_ptr(), y.data_ptr(), 512, int(purlin.DataType.BF16), 1, 77, 0xC0FFEE)
+    purlin.all_gather(x, y, h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["nbytes"]) == (1, 512)
+    purlin.all_gather_v(x, y, [32, 64, 96, 128], h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["sizes"]) == (2, [32, 64, 96, 128])
+    purlin.reduce_scatter(x, y, h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["nbytes"]) == (3, 128)          # total bytes / world
+    purlin.reduce_scatter_v(x.float(), y.float(), [32, 32, 32, 32], h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["dtype"]) == (4, int(purlin.DataType.FP32))
+    purlin.all_to_all(x, y, h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["nbytes"]) == (5, 128)
+    purlin.all_to_all_v(x, y, [32, 0, 64, 32, 0, 32, 32, 64], h, 5)
+    assert (lib.calls[-1]["coll"], lib.calls[-1]["sizes"], lib.calls[-1]["out_sizes"]) == (6, [32, 0, 64, 32], [0, 32, 32, 64])
+
+
+def test_element_type_map_and_arch():
+    assert purlin.buffer_type(torch.float16) == purlin.DataType.FP16
+    assert purlin.buffer_type(torch.float8_e4m3fn) == purlin.DataType.FP8_E4M3
+    assert purlin.buffer_type(torch.float8_e5m2) == purlin.DataType.FP8_E5M2
+    with pytest.raises(TypeError):
+        purlin.buffer_type(torch.int32)
+    assert [purlin.normalize_arch(a) for a in (70, 80, 90, 100, 103)] == [700, 800, 900, 1000, 1000]
+
+
+def test_rejections():
+    lib, h = make_handle()
+    x = torch.zeros(8, 8)
+    with pytest.raises(ValueError):
+        purlin.all_reduce(x.t(), x, h, 0)                      # non-contiguous
+    with pytest.raises(ValueError):
+        purlin.all_reduce(x, x, h, 0, reduction_mode=7)         # not a ReductionMode
+    with pytest.raises(ValueError):
+        purlin.all_gather_v(x, x, [32], h, 0)                   # one entry per rank
+    with pytest.raises(ValueError):
+        purlin.all_to_all_v(x, x, [32] * 4, h, 0)
+    assert not lib.calls
+
+
+def test_finalize_is_idempotent_and_blocks_later_calls():
+    lib, h = make_handle()
+    purlin.finalize(h, 3)
+    purlin.finalize(h, 3)
+    assert lib.destroyed == 1 and h.ctx is None and h.buf is None and h.hdl is None
+    with pytest.raises(RuntimeError):
+        purlin.all_reduce(torch.zeros(8), torch.zeros(8), h, 0)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_initialize_asks_for_the_reference_workspace_and_forwards_multicast(monkeypatch, world):
+    import torch.distributed as dist
+    from purlin_b200 import tuning
+    from purlin_b200.parallel import symmetric
+    lib = RecordingLib()
+    asked = {}
+
+    def fake_alloc(nbytes, device, group, provider=None):
+        asked["nbytes"] = nbytes
+        return "buf", "hdl", [0x1000 * (q + 1) for q in range(world)], 0xABC000
+
+    monkeypatch.setattr(dist, "get_rank", lambda g=None: 1)
+    monkeypatch.setattr(dist, "get_world_size", lambda g=None: world)
+    monkeypatch.setattr(symmetric, "allocate_symmetric", fake_alloc)
+    monkeypatch.setattr(_native, "cuda", lambda: lib)
+    monkeypatch.setattr(tuning, "load_for", lambda *a, **k: None)
+    monkeypatch.setattr(torch.cuda, "get_device_name", lambda d=None: "NVIDIA B200")
+    h = purlin.initialize("group", torch.device("cuda", 0), 100, 1234)
+    staging = 2 * (purlin.STAGING_BUFFER_SIZE + purlin.PACKET_EPOCH_BYTES)
+    assert staging == 528 << 20                                           # the reference's 528 MiB of staging
+    assert asked["nbytes"] >= staging + 3 * world * 8 + 2 * world * 16 and asked["nbytes"] < staging + 4096
+    c = lib.calls[0]
+    assert c["create"] and c["rank"] == 1 and c["world"] == world and c["mc"] == 0xABC000 and c["stream"] == 1234
+    assert c["ptrs"] == [0x1000 * (q + 1) for q in range(world)] and c["staging"] == purlin.STAGING_BUFFER_SIZE
+    assert h.ctx == 0xC0FFEE and h.buf == "buf" and h.has_multicast
