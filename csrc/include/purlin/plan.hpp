@@ -89,4 +89,18 @@ struct Plan {
   Step steps[kMaxSteps];
 };
 
+// Aligned even split with the remainder spread over the first parts
+// (behaviour of partition<Align>, csrc/include/purlin/partition.cuh:217-247).
+struct Span { size_t offset; size_t bytes; };
+PURLIN_HD inline Span partitionAligned(size_t bytes, int parts, int index, size_t align) {
+  const size_t units = bytes / align;        // whole aligned units
+  const size_t tail = bytes - units * align; // goes to the last non-empty part
+  const size_t base = units / size_t(parts), rem = units % size_t(parts);
+  const size_t i = size_t(index);
+  const size_t begin = (i * base + (i < rem ? i : rem)) * align;
+  size_t len = (base + (i < rem ? 1 : 0)) * align;
+  if (index == parts - 1) len += tail;
+  return Span{begin, len};
+}
+
 }  // namespace purlin

@@ -29,3 +29,18 @@ def test_moe_all_gpus():
     sys.stdout.write(res.stdout[-3000:])
     sys.stderr.write(res.stderr[-3000:])
     assert res.returncode == 0
+
+
+def test_moe_block_world_of_one_matches_fp32_reference():
+    from purlin_b200.models.moe_block import ExpertParallelMoE
+    moe = ExpertParallelMoE(hidden=512, intermediate=256, experts=32, topk=4, max_tokens=256, device="cuda:0", capacity_factor=4.0)
+    g = torch.Generator(device="cuda:0").manual_seed(5)
+    x = torch.randn(256, 512, generator=g, device="cuda:0").to(torch.bfloat16)
+    y = moe(x)
+    moe.ep.check()
+    ref = moe.reference(x)
+    err = (y.float() - ref).abs().max().item()
+    assert err <= 3e-2 * ref.abs().max().item() + 2e-3, err
+    y2 = moe(x)            # a second layer call reuses the buffers
+    moe.ep.check()
+    assert torch.equal(y, y2)
