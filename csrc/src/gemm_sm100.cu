@@ -123,9 +123,8 @@ PURLIN_D int rowBlockOf(const Params& p, int mIdx) {
   }
 }
 
-// Tile t -> (row-block index, column block). Fused variants walk a row block's columns first (blocks become
-// usable in arrival order). The plain GEMM walks bands of kGroupM row blocks, rows fastest inside a band, so the
-// tiles in flight at one time share a few A blocks and a few B blocks and the working set stays inside L2.
+// Tile t -> (row-block index, column block). Tiles are walked in bands of kGroupM row blocks, rows fastest inside a
+// band, so the tiles in flight at one time share a few A blocks and a few B blocks and the working set stays in L2.
 constexpr int kGroupM = 8;
 template <int COMM>
 PURLIN_D void tileCoord(const Params& p, int t, int& mIdx, int& nBlk) {
@@ -137,10 +136,19 @@ PURLIN_D void tileCoord(const Params& p, int t, int& mIdx, int& nBlk) {
     mIdx = first + within % rows;
     nBlk = within / rows;
   } else {
-    mIdx = t / p.tilesN;
-    nBlk = t % p.tilesN;
+    // the same banding inside one rank's rows (a rank's row blocks become usable together: they arrive, or are
+    // owed, as one phase), phases in the order rowBlockOf() gives them
+    const int perRank = p.blocksPerRank * p.tilesN;
+    const int seg = t / perRank, u = t - seg * perRank;
+    const int perBand = kGroupM * p.tilesN;
+    const int band = u / perBand, within = u - band * perBand;
+    const int first = band * kGroupM;
+    const int rows = p.blocksPerRank - first < kGroupM ? p.blocksPerRank - first : kGroupM;
+    mIdx = seg * p.blocksPerRank + first + within % rows;
+    nBlk = within / rows;
   }
 }
+
 
 // CTAS = 1: every CTA owns 128 x bn tiles. CTAS = 2: a cluster of two CTAs owns 256 x bn tiles; each CTA loads its
 // 128 rows of A and its half of B's columns, CTA 0 issues one 256-row MMA for the pair (cta_group::2), so every
