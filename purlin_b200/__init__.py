@@ -276,3 +276,18 @@ def build_plan(collective, world, rank, nbytes=0, sizes=None, out_sizes=None, dt
 
 
 Policy = _native.Policy
+
+
+def symm_empty(shape, dtype, handle_or_group=None, device=None):
+    """Allocates a tensor in symmetric memory (collective over the group). See ``all_reduce_symm``."""
+    from .parallel.symmetric import SymmetricTensor
+    group = getattr(handle_or_group, "group", handle_or_group)
+    dev = device or getattr(handle_or_group, "device", None) or torch.device("cuda", torch.cuda.current_device())
+    return SymmetricTensor(shape, dtype, dev, group)
+
+
+def all_reduce_symm(symm_tensor, op: ReduceOp = ReduceOp.ADD, reduction_mode=ReductionMode.NON_DETERMINISTIC, blocks: int = 0):
+    """In-place all-reduce of a ``symm_empty`` tensor with no staging copies: the NVSwitch reduces every rank's shard
+    straight out of the tensors and broadcasts it straight back (plain peer loads/stores when there is no multicast
+    alias or the mode is deterministic)."""
+    return symm_tensor.all_reduce_(int(op), _mode(reduction_mode), blocks)

@@ -107,3 +107,53 @@ def allocate_emulated(nbytes: int, world: int, device: torch.device) -> Tuple[li
     """``world`` zeroed blocks on one device; every virtual rank sees the same pointer list."""
     blocks = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
     return blocks, [b.data_ptr() for b in blocks]
+
+
+class SymmetricTensor:
+    """A tensor in symmetric memory together with its peer mappings and the flag block the zero-copy collectives use.
+
+    ``tensor`` is an ordinary torch view of this rank's memory; fill it with any kernel, then call
+    ``purlin_b200.all_reduce_symm`` to reduce it in place across the group without staging copies.
+    """
+
+    def __init__(self, shape, dtype, device, group=None, provider: str | None = None):
+        import math
+        import torch.distributed as dist
+        from .. import _native
+        self.lib = _native.cuda()
+        self.lib.purlin_symm_flag_bytes.restype = C.c_size_t
+        self.lib.purlin_symm_flag_bytes.argtypes = [C.c_int]
+        self.lib.purlin_symm_all_reduce.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64),
+                                                    C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_void_p]
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.device(device)
+        self.dtype = dtype
+        numel = int(math.prod(shape)) if not isinstance(shape, int) else int(shape)
+        self.nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if self.nbytes % 32:
+            raise ValueError("symmetric tensors must be a multiple of 32 bytes")
+        data_bytes = (self.nbytes + 255) // 256 * 256
+        flag_bytes = int(self.lib.purlin_symm_flag_bytes(self.world))
+        self._owner, self._hdl, ptrs, mc = allocate_symmetric(data_bytes + flag_bytes, self.device, group, provider)
+        self.data_ptrs = (C.c_uint64 * self.world)(*ptrs)
+        self.flag_ptrs = (C.c_uint64 * self.world)(*[p + data_bytes for p in ptrs])
+        self.multicast_ptr = int(mc or 0)
+        from .expert_parallel import _RawBuffer
+        raw = torch.as_tensor(_RawBuffer(ptrs[self.rank], (self.nbytes,), "|u1"), device=self.device)
+        self.tensor = raw.view(dtype).view(shape)
+
+    def all_reduce_(self, op: int = 0, mode: int = 0, blocks: int = 0, mm_depth: int = 8, timeout_ms: int = 10000):
+        from .. import _native, buffer_type
+        rc = self.lib.purlin_symm_all_reduce(self.rank, self.world, self.data_ptrs, self.multicast_ptr, self.flag_ptrs, self.nbytes,
+                                             int(buffer_type(self.dtype)), int(op), int(mode), blocks, mm_depth,
+                                             timeout_ms * 1_000_000, torch.cuda.current_stream().cuda_stream)
+        _native.check(self.lib, rc)
+        return self.tensor
+
+    def status(self) -> int:
+        """Synchronises and returns the status word of the flag block (0 = healthy)."""
+        torch.cuda.synchronize(self.device)
+        from .expert_parallel import _RawBuffer
+        words = torch.as_tensor(_RawBuffer(int(self.flag_ptrs[self.rank]), (2 * self.world + 4,), "<i8"), device=self.device)
+        return int(words[2 * self.world + 2].item() & 0xffffffff)

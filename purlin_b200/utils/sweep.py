@@ -89,6 +89,7 @@ def main():
     ap.add_argument("--graph", type=int, default=0)
     ap.add_argument("--tune", action="store_true")
     ap.add_argument("--no-nccl", action="store_true")
+    ap.add_argument("--symm", action="store_true", help="also time the zero-copy all-reduce on symmetric tensors")
     ap.add_argument("--csv", default="")
     ap.add_argument("--table-out", default="")
     args = ap.parse_args()
@@ -199,6 +200,16 @@ def main():
                 if rank == 0:
                     print(bench.csv_row(coll, "purlin_b200", world, total, args.dtype, t, 0.0 if ok else 100.0), flush=True)
                     rows.append((coll, "purlin_b200", n, t.us))
+            if coll == "ar" and args.symm and not args.tune:
+                # zero-copy variant: the tensor lives in symmetric memory, no staging passes
+                stt = purlin.symm_empty((in_b // esz,), td, h)
+                stt.tensor.copy_(x)
+                purlin.all_reduce_symm(stt)
+                oks = torch.equal(stt.tensor, expect) and stt.status() == 0
+                t = bench.measure(lambda: purlin.all_reduce_symm(stt), args.warmup, runs, args.graph)
+                if rank == 0:
+                    print(bench.csv_row(coll, "purlin_b200:symm-zero-copy", world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
+                del stt
             if not args.no_nccl:
                 t = bench.measure(nccl_timed, args.warmup, runs, args.graph)
                 if rank == 0:

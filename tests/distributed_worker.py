@@ -138,6 +138,22 @@ def main():
     purlin.check(h)
     if not torch.all(out == W).item():
         failures.append("back-to-back all-reduce")
+    # zero-copy all-reduce on a tensor allocated in symmetric memory (NVLS when offered, peer loads otherwise)
+    for dtype, n in ((torch.bfloat16, 1 << 20), (torch.float32, 32 * W * 9)):
+        st = purlin.symm_empty((n,), dtype, h)
+        for mode in (purlin.ReductionMode.NON_DETERMINISTIC, purlin.ReductionMode.DETERMINISTIC):
+            for rep in range(2):
+                parts = [ints(n, 0 if dtype == torch.bfloat16 else 4, 900 + rep * 10 + r) for r in range(W)]
+                st.tensor.copy_(parts[rank].to(dev))
+                purlin.all_reduce_symm(st, reduction_mode=mode)
+                if st.status() != 0:
+                    failures.append(f"symm all-reduce {dtype} mode {int(mode)}: status {st.status()}")
+                    break
+                exp = expected(AR, W, rank, parts, n * parts[0].element_size(), None, 0 if dtype == torch.bfloat16 else 4)
+                if not torch.equal(st.tensor.cpu().view(torch.uint8), exp.view(torch.uint8)):
+                    failures.append(f"symm all-reduce {dtype} mode {int(mode)} rep {rep}")
+        count += 1
+        del st
     purlin.finalize(h)
     purlin.finalize(h)
     ok = torch.tensor([0 if failures else 1], device=dev)
