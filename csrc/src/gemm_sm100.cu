@@ -107,6 +107,22 @@ PURLIN_D float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 PURLIN_D float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 PURLIN_D float silu(float x) { return x / (1.f + __expf(-x)); }
 
+// 32 fp32 accumulator values of one row -> bf16 -> global (or peer) memory. Two 32-byte stores when the row pitch
+// keeps them aligned (whole sectors, and NVLink-friendly when `out` is peer memory), 16-byte stores otherwise.
+PURLIN_D void storeChunkBf16(__nv_bfloat16* out, const uint32_t (&r)[32], int col, int N, bool wide) {
+  uint32_t o[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) o[i] = packBf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+  if (wide && col + 32 <= N) {
+    st32(out, Vec32{{o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]}});
+    st32(out + 16, Vec32{{o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]}});
+  } else {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      if (col + g * 8 + 8 <= N) st16(out + g * 8, Vec16{{o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]}});
+  }
+}
+
 // order in which (CTAS x 128)-row blocks are visited
 template <int COMM>
 PURLIN_D int rowBlockOf(const Params& p, int mIdx) {
@@ -344,8 +360,8 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
             }
             __nv_bfloat16* out = p.C + size_t(row) * p.ldc + col / 2;
             if (col / 2 + 16 <= p.ldc) {
-              st16(out, Vec16{{o[0], o[1], o[2], o[3]}});
-              st16(out + 8, Vec16{{o[4], o[5], o[6], o[7]}});
+              if ((reinterpret_cast<uintptr_t>(out) & 31u) == 0) st32(out, Vec32{{o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]}});
+              else { st16(out, Vec16{{o[0], o[1], o[2], o[3]}}); st16(out + 8, Vec16{{o[4], o[5], o[6], o[7]}}); }
             }
           }
         } else if constexpr (COMM == kCommRS) {
@@ -374,20 +390,12 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
             __nv_bfloat16* out = (dstRank == p.rank)
                 ? p.C + size_t(rowInShard) * p.ldc + col      // world of one: plain store
                 : p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride + (size_t(p.rank) * perRank * kBM + rowInShard) * p.N + col;
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              if (col + g * 8 + 8 <= p.N)
-                st16(out + g * 8, Vec16{{packBf16(__uint_as_float(r[g * 8]), __uint_as_float(r[g * 8 + 1])), packBf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3])),
-                                         packBf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5])), packBf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]))}});
+            storeChunkBf16(out, r, col, p.N, (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
           }
         } else {
           if (row < p.M) {
             __nv_bfloat16* out = p.C + size_t(row) * p.ldc + col;
-#pragma unroll
-            for (int g = 0; g < 4; ++g)
-              if (col + g * 8 + 8 <= p.N)
-                st16(out + g * 8, Vec16{{packBf16(__uint_as_float(r[g * 8]), __uint_as_float(r[g * 8 + 1])), packBf16(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3])),
-                                         packBf16(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5])), packBf16(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]))}});
+            storeChunkBf16(out, r, col, p.N, (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
           }
         }
       }
