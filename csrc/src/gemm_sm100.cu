@@ -74,6 +74,7 @@ struct Params {
   uint64_t* rowReady[kMaxRanks];       // every rank's flags, [tilesM]
   uint32_t* pushCounters;              // local last-arrival counters, [(world - 1) * blocksPerRank]
   int pushParts;                       // pieces one 128-row block is split into for pushing
+  int commWarps;                       // how many of a CTA's communication warps take part (1..4): paces the pushes
   size_t gatherParityBytes;            // bytes between the gather buffers of even and odd calls
   // GEMM -> reduce-scatter
   __nv_bfloat16* partialBuf[kMaxRanks];// every rank's receive buffers: 2 parities x [world slots][M / world, N]
@@ -366,26 +367,43 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           }
         } else if constexpr (COMM == kCommRS) {
           if (reduceOwn) {
-            // ascending rank order; own accumulator takes this rank's place in the sum
+            // ascending rank order; own accumulator takes this rank's place in the sum. All peers' copies of the
+            // 32 columns are requested before any is consumed (up to 8 peers x 64 bytes in flight per thread).
+            float acc[32];
 #pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              if (col + g * 8 + 8 > p.N) break;
-              float acc[8];
+            for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+            const bool full = col + 32 <= p.N;
+            for (int q0 = 0; q0 < p.world; q0 += 8) {
+              Vec16 v[8][4];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-              for (int q = 0; q < p.world; ++q) {
-                if (q == p.rank) {
+              for (int b = 0; b < 8; ++b)
+                if (q0 + b < p.world && q0 + b != p.rank) {
+                  const __nv_bfloat16* src = partialBase + size_t(q0 + b) * slotStride + col;
 #pragma unroll
-                  for (int e = 0; e < 8; ++e) acc[e] += __uint_as_float(r[g * 8 + e]);
+                  for (int g = 0; g < 4; ++g)
+                    if (full || col + g * 8 + 8 <= p.N) v[b][g] = ld16(src + g * 8);
+                }
+#pragma unroll
+              for (int b = 0; b < 8; ++b) {
+                if (q0 + b >= p.world) break;
+                if (q0 + b == p.rank) {
+#pragma unroll
+                  for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(r[e]);
                 } else {
-                  const Vec16 v = ld16(partialBase + size_t(q) * slotStride + col + g * 8);
 #pragma unroll
-                  for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16lo(v.x[e]); acc[2 * e + 1] += bf16hi(v.x[e]); }
+                  for (int g = 0; g < 4; ++g)
+                    if (full || col + g * 8 + 8 <= p.N) {
+#pragma unroll
+                      for (int e = 0; e < 4; ++e) { acc[g * 8 + 2 * e] += bf16lo(v[b][g].x[e]); acc[g * 8 + 2 * e + 1] += bf16hi(v[b][g].x[e]); }
+                    }
                 }
               }
-              st16(p.C + size_t(rowInShard) * p.ldc + col + g * 8,
-                   Vec16{{packBf16(acc[0], acc[1]), packBf16(acc[2], acc[3]), packBf16(acc[4], acc[5]), packBf16(acc[6], acc[7])}});
             }
+            uint32_t accBits[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) accBits[e] = __float_as_uint(acc[e]);
+            __nv_bfloat16* out = p.C + size_t(rowInShard) * p.ldc + col;
+            storeChunkBf16(out, accBits, col, p.N, (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
           } else {
             __nv_bfloat16* out = (dstRank == p.rank)
                 ? p.C + size_t(rowInShard) * p.ldc + col      // world of one: plain store
@@ -420,7 +438,8 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
   } else {
     // ------------------------------- communication warps (all-gather push) -------------------------------
     if constexpr (COMM == kCommAG) {
-      const int ct = threadIdx.x - 32 * (2 + kEpiWarps), cn = 32 * kCommWarps;
+      const int ct = threadIdx.x - 32 * (2 + kEpiWarps), cn = 32 * p.commWarps;   // p.commWarps of the 4 warps push
+      if (ct < cn) {
       const int perRank = p.blocksPerRank * CTAS;
       const size_t blockBytes = size_t(kBM) * p.K * 2;
       const int items = (p.world - 1) * perRank * p.pushParts;
@@ -443,6 +462,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
         asm volatile("bar.sync 1, %0;" ::"r"(cn) : "memory");
         if (ct == 0 && sig::lastArrival(p.pushCounters + unit, uint32_t(p.pushParts)))
           sig::stReleaseSys(p.rowReady[peer] + size_t(p.rank) * perRank + b, epoch);
+      }
       }
     }
   }
@@ -672,6 +692,13 @@ int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, voi
   p.status = reinterpret_cast<uint32_t*>(lb + 256); p.timeoutNs = c->timeoutNs;
   p.pushCounters = reinterpret_cast<uint32_t*>(lb + 4096);
   p.pushParts = 8;
+  {
+    // Few pushing warps per CTA pace the remote stores: a saturated NVLink store queue stalls every memory
+    // instruction of its SM, the epilogue's included. PURLIN_AG_COMM_WARPS overrides (1..4).
+    const char* e = std::getenv("PURLIN_AG_COMM_WARPS");
+    p.commWarps = e ? std::min(std::max(std::atoi(e), 1), kCommWarps) : 1;
+    if (const char* pp = std::getenv("PURLIN_AG_PUSH_PARTS")) p.pushParts = std::min(std::max(std::atoi(pp), 1), 64);
+  }
   p.localA = static_cast<const __nv_bfloat16*>(xLocal);
   p.C = static_cast<__nv_bfloat16*>(out); p.ldc = epilogue == kEpiSwiglu ? N / 2 : N;
   // the host cannot know the device epoch (graph replays advance it): pass the maps of both gather buffers
