@@ -53,6 +53,8 @@ constexpr int kThreadsComm = 32 * (2 + kEpiWarps + kCommWarps);
 constexpr int kSmemBudget = 227 * 1024;
 constexpr int kBarrierBytes = 256;
 constexpr int kMaxStages = 8;
+constexpr int kScratchPitch = 272;              // bytes per row of the epilogue's transpose scratch (256 + 16: conflict-free)
+constexpr int kScratchBytes = kEpiWarps * 32 * kScratchPitch;   // reduce-scatter variant only
 
 enum { kEpiStore = 0, kEpiSwiglu = 1 };
 enum { kCommNone = 0, kCommAG = 1, kCommRS = 2 };
@@ -80,6 +82,7 @@ struct Params {
   __nv_bfloat16* partialBuf[kMaxRanks];// every rank's receive buffers: 2 parities x [world slots][M / world, N]
   uint64_t* tileReady[kMaxRanks];      // every rank's flags, [world][blocksPerRank][tilesN][4 row quarters]
   size_t partialParityStride;          // elements between the two parities
+  int rsScratch;                       // 1: remote tiles leave through a shared-memory transpose (long contiguous runs per row)
 };
 
 struct alignas(64) Maps { CUtensorMap a, b, aLocal, a1; };   // a1: gather buffer of odd calls (all-gather variant)
@@ -107,6 +110,15 @@ PURLIN_D uint32_t packBf16(float lo, float hi) {
 PURLIN_D float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 PURLIN_D float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
 PURLIN_D float silu(float x) { return x / (1.f + __expf(-x)); }
+
+PURLIN_D void stShared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+PURLIN_D Vec16 ldShared16(uint32_t addr) {
+  Vec16 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x[0]), "=r"(v.x[1]), "=r"(v.x[2]), "=r"(v.x[3]) : "r"(addr) : "memory");
+  return v;
+}
 
 // 32 fp32 accumulator values of one row -> bf16 -> global (or peer) memory. Two 32-byte stores when the row pitch
 // keeps them aligned (whole sectors, and NVLink-friendly when `out` is peer memory), 16-byte stores otherwise.
@@ -344,7 +356,44 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
         }
       }
 
-      for (int c0 = 0; c0 < p.bn; c0 += 32) {
+      bool viaScratch = false;
+      if constexpr (COMM == kCommRS && EPI == kEpiStore) {
+        viaScratch = p.rsScratch && dstRank != p.rank && p.bn % 128 == 0 && n0 + p.bn <= p.N;
+        if (viaScratch) {
+          // Rows of a remote tile leave as 128-byte runs: the 32 lanes hold 32 different rows (64 bytes each per TMEM
+          // load), so a direct store would put 32 separate 32-byte sectors on NVLink per instruction. Through the
+          // scratch each store instruction writes 4 rows x 128 contiguous bytes.
+          const uint32_t scratch = barBase + kBarrierBytes + uint32_t(warp - 2) * 32u * kScratchPitch;
+          __nv_bfloat16* tileOut = p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride +
+                                   (size_t(p.rank) * perRank * kBM + size_t(rowInShard - lane)) * p.N + n0;   // row of lane 0
+          for (int h0 = 0; h0 < p.bn; h0 += 128) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t r[32];
+              tc::tmemLoad32(taddr + uint32_t(h0 + c * 32), r);
+              tc::tmemLoadWait();
+              const uint32_t rowAddr = scratch + uint32_t(lane) * kScratchPitch + uint32_t(c) * 64u;
+#pragma unroll
+              for (int g = 0; g < 4; ++g)
+                stShared16(rowAddr + g * 16, packBf16(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1])), packBf16(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3])),
+                           packBf16(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5])), packBf16(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7])));
+            }
+            __syncwarp();
+            const int rowInGroup = lane >> 3, piece = lane & 7;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = 4 * i + rowInGroup;
+              const uint32_t src = scratch + uint32_t(rr) * kScratchPitch + uint32_t(piece) * 16u;
+              const Vec16 lo = ldShared16(src), hi = ldShared16(src + 128);
+              __nv_bfloat16* o = tileOut + size_t(rr) * p.N + h0;
+              st16(o + piece * 8, lo);
+              st16(o + 64 + piece * 8, hi);
+            }
+            __syncwarp();
+          }
+        }
+      }
+      for (int c0 = 0; c0 < p.bn && !viaScratch; c0 += 32) {
         uint32_t r[32];
         tc::tmemLoad32(taddr + uint32_t(c0), r);
         tc::tmemLoadWait();
@@ -545,7 +594,7 @@ int ctasFor(int M, int rowsPerRank) {
   return (rowsPerRank % (2 * kBM) == 0 && M >= 2 * kBM) ? 2 : 1;
 }
 
-bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas) {
+bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas, int scratchBytes = 0) {
   if (M <= 0 || N <= 0 || K <= 0) { setError("GEMM dimensions must be positive"); return false; }
   if (K % 8 || N % 8) { setError("N and K must be multiples of 8"); return false; }
   if (bn == 0) bn = chooseBn(M, N, epilogue);
@@ -554,10 +603,10 @@ bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas) {
   if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
   p.tilesM = (M + kBM * ctas - 1) / (kBM * ctas); p.tilesN = (N + bn - 1) / bn;
   const int stageBytes = kABytes + (bn / ctas) * kBK * 2;
-  p.stages = std::min((kSmemBudget - kBarrierBytes - 1024) / stageBytes, kMaxStages);
+  p.stages = std::min((kSmemBudget - kBarrierBytes - 1024 - scratchBytes) / stageBytes, kMaxStages);
   return true;
 }
-size_t smemFor(const Params& p, int ctas) { return size_t(p.stages) * (kABytes + (p.bn / ctas) * kBK * 2) + kBarrierBytes + 1024; }
+size_t smemFor(const Params& p, int ctas) { return size_t(p.stages) * (kABytes + (p.bn / ctas) * kBK * 2) + kBarrierBytes + 1024 + (p.rsScratch ? kScratchBytes : 0); }
 
 template <int EPI, int COMM, int CTAS>
 int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
@@ -720,7 +769,9 @@ int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* ou
   if (M > c->M || N > c->nRs || M % (c->world * kBM)) { setError("GEMM reduce-scatter shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
   const int ctas = ctasFor(M, M / c->world);
-  if (!fillShape(p, M, N, K, kEpiStore, 0, ctas)) return 1;
+  const int scratch = std::getenv("PURLIN_RS_DIRECT_STORES") ? 0 : 1;
+  if (!fillShape(p, M, N, K, kEpiStore, 0, ctas, scratch ? kScratchBytes : 0)) return 1;
+  p.rsScratch = scratch;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
   p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * ctas);
   p.epoch = reinterpret_cast<uint64_t*>(lb + 128); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 192);
