@@ -235,6 +235,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
     // ------------------------------- TMA producer -------------------------------
     if (lane == 0) {
       uint32_t st = 0, ph = 0;          // ring position and its phase
+      uint64_t seenReady = 0;           // row blocks whose arrival flag this thread has already acquired
       bool ok = true;
       for (int t = pairIdx; t < numTiles && ok; t += numPairs) {
         int mIdx, nBlk;
@@ -252,9 +253,12 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           } else {
             // rows pushed by a peer: wait for the block's flag, then order those generic-proxy writes
             // before this thread's async-proxy reads (TMA)
-            ok = waitFlag(p.rowReady[p.rank] + mBlk, epoch, abortWord, p.timeoutNs);
-            if (!ok) { recordTimeout(p, 4, mBlk, 0); break; }
-            tc::fenceProxyAsync();
+            if (mBlk >= 64 || !((seenReady >> mBlk) & 1ull)) {   // a block seen once stays ready for the whole call
+              ok = waitFlag(p.rowReady[p.rank] + mBlk, epoch, abortWord, p.timeoutNs);
+              if (!ok) { recordTimeout(p, 4, mBlk, 0); break; }
+              tc::fenceProxyAsync();
+              if (mBlk < 64) seenReady |= 1ull << mBlk;
+            }
           }
         }
         for (int kb = 0; kb < kBlocks; ++kb) {
