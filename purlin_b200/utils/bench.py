@@ -118,7 +118,7 @@ def parse_size(s: str) -> int:
 class ClockSampler:
     """Samples SM clocks and throttle reasons through NVML while a timed region runs (read-only)."""
 
-    def __init__(self, index: int = 0, period_s: float = 0.2):
+    def __init__(self, index: int = 0, period_s: float = 0.005):
         import threading
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
