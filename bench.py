@@ -49,6 +49,7 @@ def run_reference(args):
         print(json.dumps(out), flush=True)
         return
     import subprocess
+    import tempfile
     code = (
         "import sys; sys.path.insert(0, %r)\n"
         "import purlin\n"
@@ -60,7 +61,7 @@ def run_reference(args):
     )
     try:
         res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=240,
-                             env=dict(os.environ, PURLIN_CACHE_DIR=os.path.join(ROOT, "gpurun_out", "ref_jit_cache")))
+                             env=dict(os.environ, PURLIN_CACHE_DIR=tempfile.mkdtemp(prefix="purlin_ref_jit_")))
         if res.returncode == 0 and "built" in res.stdout:
             out["unavailable"] = ("reference binding built, but the reference has no fused tensor-parallel GEMM "
                                   "(its tree contains no GEMM), so this metric cannot be measured on it")

@@ -56,7 +56,7 @@ struct Context {
   uint32_t* status;                      // [4]: code, step, peer, chunk
   size_t stagingTRSize;
   size_t packetStride;
-  uint64_t timeoutNs;                    // budget of every device wait
+  uint64_t timeoutNs;                    // time limit of every device wait
   int32_t world;
   int32_t rank;
 };

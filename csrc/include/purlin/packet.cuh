@@ -31,7 +31,7 @@ PURLIN_D void writeMulticast(Packet* mc, uint64_t data, uint64_t flag) {
                "r"(uint32_t(data)), "r"(uint32_t(data >> 32)), "r"(uint32_t(flag)), "r"(uint32_t(flag >> 32))
                : "memory");
 }
-// Spin until the packet carries `flag`; false when the budget ran out.
+// Spin until the packet carries `flag`; false when the time limit ran out.
 PURLIN_D bool read(const Context& ctx, const Packet* p, uint64_t flag, uint64_t& data,
                    uint32_t code, uint32_t step, uint32_t peer) {
   Packet v = load(p);

@@ -4,7 +4,7 @@
 // followed by an acquire load, release store of a monotonic flag into peer
 // memory, self-resetting arrival counter). The difference that matters: the
 // reference spins forever, so a missing peer hangs the GPU. Every wait here
-// carries a time budget; when it runs out the waiter records where it gave up
+// carries a time limit; when it runs out the waiter records where it gave up
 // in the context's status word and the whole call unwinds.
 #pragma once
 #include <cuda_runtime.h>
@@ -53,7 +53,7 @@ PURLIN_D void fail(const Context& ctx, uint32_t code, uint32_t step, uint32_t pe
 
 PURLIN_D bool failed(const Context& ctx) { return ldRelaxedGpu32(ctx.status) != 0u; }
 
-// Spin until *flag >= value. Returns false when the budget ran out or another
+// Spin until *flag >= value. Returns false when the time limit ran out or another
 // CTA of this call already failed. Called by single threads, not whole CTAs.
 PURLIN_D bool waitAtLeast(const Context& ctx, const uint64_t* flag, uint64_t value,
                           uint32_t code, uint32_t step, uint32_t peer, uint32_t chunk) {

@@ -2,7 +2,7 @@
 // loads (never with cluster multicast), TMEM allocation, tcgen05.mma / commit / ld.
 //
 // No counterpart in the reference (it contains no tensor-core code at all). Every
-// wait on an mbarrier is bounded: when the budget runs out the waiter raises the
+// wait on an mbarrier is bounded: when the time limit runs out the waiter raises the
 // CTA's abort word, records a status and the kernel unwinds, frees its TMEM and returns.
 #pragma once
 #include <cuda.h>

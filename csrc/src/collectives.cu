@@ -346,13 +346,13 @@ int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collect
       // the built-in policy sizes grids for a whole GPU per rank; here `world` ranks share one
       int sms = 148;
       cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctxs[r]->device);
-      const int budget = std::max(sms / world, 2);
+      const int perRank = std::max(sms / world, 2);
       fitted = selectPolicy(spec, ctxs[r]->ws);
       fitted.putBlocks = std::min(fitted.putBlocks, world);
       fitted.gatherBlocks = std::min(fitted.gatherBlocks, world - 1);
       fitted.localBlocks = 1;
-      fitted.consumeBlocks = std::min(fitted.consumeBlocks, std::max(budget - 2 * world, 1));
-      fitted.lrBlocks = std::min(fitted.lrBlocks, budget);
+      fitted.consumeBlocks = std::min(fitted.consumeBlocks, std::max(perRank - 2 * world, 1));
+      fitted.lrBlocks = std::min(fitted.lrBlocks, perRank);
       use = &fitted;
     }
     if (!planFor(spec, ctxs[r]->ws, use, host[r].plan, nullptr)) return 1;

@@ -50,7 +50,7 @@ constexpr int kABytes = kBM * kBK * 2;         // 16 KiB
 constexpr int kEpiWarps = 4, kCommWarps = 4;
 constexpr int kThreadsPlain = 32 * (2 + kEpiWarps);
 constexpr int kThreadsComm = 32 * (2 + kEpiWarps + kCommWarps);
-constexpr int kSmemBudget = 227 * 1024;
+constexpr int kSmemLimit = 227 * 1024;
 constexpr int kBarrierBytes = 256;
 constexpr int kMaxStages = 8;
 constexpr int kScratchPitch = 272;              // bytes per row of the epilogue's transpose scratch (256 + 16: conflict-free)
@@ -607,7 +607,7 @@ bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas, i
   if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
   p.tilesM = (M + kBM * ctas - 1) / (kBM * ctas); p.tilesN = (N + bn - 1) / bn;
   const int stageBytes = kABytes + (bn / ctas) * kBK * 2;
-  p.stages = std::min((kSmemBudget - kBarrierBytes - 1024 - scratchBytes) / stageBytes, kMaxStages);
+  p.stages = std::min((kSmemLimit - kBarrierBytes - 1024 - scratchBytes) / stageBytes, kMaxStages);
   return true;
 }
 size_t smemFor(const Params& p, int ctas) { return size_t(p.stages) * (kABytes + (p.bn / ctas) * kBK * 2) + kBarrierBytes + 1024 + (p.rsScratch ? kScratchBytes : 0); }
@@ -618,14 +618,14 @@ int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
   constexpr int threads = COMM == kCommAG ? kThreadsComm : kThreadsPlain;
   static int maxClusters = -1;
   if (maxClusters < 0) {
-    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget) != cudaSuccess) { setError("cannot opt in to 227 KiB of shared memory"); return 1; }
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) { setError("cannot opt in to 227 KiB of shared memory"); return 1; }
     maxClusters = smCount() / CTAS;
     if (CTAS == 2) {
       // pairs must sit on SMs of one GPC: ask how many pairs the device can hold at once
       cudaLaunchConfig_t q{};
       cudaLaunchAttribute qa[1];
       qa[0].id = cudaLaunchAttributeClusterDimension; qa[0].val.clusterDim.x = 2; qa[0].val.clusterDim.y = 1; qa[0].val.clusterDim.z = 1;
-      q.gridDim = dim3(smCount() / 2 * 2); q.blockDim = dim3(threads); q.dynamicSmemBytes = kSmemBudget; q.attrs = qa; q.numAttrs = 1;
+      q.gridDim = dim3(smCount() / 2 * 2); q.blockDim = dim3(threads); q.dynamicSmemBytes = kSmemLimit; q.attrs = qa; q.numAttrs = 1;
       int n = 0;
       if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) == cudaSuccess && n > 0) maxClusters = std::min(maxClusters, n);
     }

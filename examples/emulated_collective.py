@@ -17,9 +17,9 @@ in_b = n if coll in (0, 1) else n * world
 out_b = n * world if coll in (1, 5) else n
 srcs = [torch.full((in_b // 2,), float(r + 1), dtype=torch.bfloat16, device="cuda") for r in range(world)]
 dsts = [torch.zeros(out_b // 2, dtype=torch.bfloat16, device="cuda") for _ in range(world)]
-budget = 148 // world
-pol = _native.Policy.from_dict(dict(regime=1, threads=256, putBlocks=max(budget // 4, world), localBlocks=2, consumeBlocks=budget // 2,
-                                    gatherBlocks=max(budget // 5, world - 1), lrBlocks=8, memType=0, mmDepth=4, unroll=8, stageDepth=0, arPath=1,
+per_rank = 148 // world
+pol = _native.Policy.from_dict(dict(regime=1, threads=256, putBlocks=max(per_rank // 4, world), localBlocks=2, consumeBlocks=per_rank // 2,
+                                    gatherBlocks=max(per_rank // 5, world - 1), lrBlocks=8, memType=0, mmDepth=4, unroll=8, stageDepth=0, arPath=1,
                                     lrMulticast=0, weighted=1, chunkBytes=4 << 20, perStreamThreshold=0))
 for _ in range(3):
     ew.run(coll, srcs, dsts, nbytes=n, dtype=0, policy=pol)

@@ -217,7 +217,7 @@ def main():
             n *= args.factor
     if args.tune and rank == 0:
         from purlin_b200 import tuning
-        path = args.table_out or os.path.join("gpurun_out", str(tuning.table_path(torch.cuda.get_device_name(), world).name))
+        path = args.table_out or os.path.join("tuning_out", str(tuning.table_path(torch.cuda.get_device_name(), world).name))
         os.makedirs(os.path.dirname(path) or ".", exist_ok=True)
         with open(path, "w") as f:
             json.dump({"gpu": torch.cuda.get_device_name(), "world": world, "dtype": args.dtype, "entries": table}, f, indent=1, sort_keys=True)
