@@ -75,6 +75,24 @@ int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collect
 /* ---- point-to-point copy through the Atom (push or pull over a peer pointer) ---- */
 int purlin_p2p_copy(void* dst, const void* src, size_t bytes, int blocks, int threads, void* stream);
 
+/* ---- native symmetric-memory provider on the CUDA virtual-memory API (+ NVLS multicast alias) ----
+ * create -> all-gather (pid, fd) -> map_peers; then, if multicast is supported on every rank:
+ * rank 0 multicast_create -> broadcast (pid, fd) -> multicast_join everywhere -> barrier -> multicast_bind -> barrier.
+ * Release: barrier -> detach everywhere -> barrier -> destroy. */
+typedef struct PurlinVmmBlock PurlinVmmBlock;
+int purlin_vmm_multicast_supported(int device);
+PurlinVmmBlock* purlin_vmm_create(int device, size_t bytes, int rank, int world);
+size_t purlin_vmm_bytes(const PurlinVmmBlock* block);
+int purlin_vmm_local_handle(const PurlinVmmBlock* block, int* pid, int* fd);
+int purlin_vmm_map_peers(PurlinVmmBlock* block, const int* pids, const int* fds);
+uint64_t purlin_vmm_peer_ptr(const PurlinVmmBlock* block, int rank);
+int purlin_vmm_multicast_create(PurlinVmmBlock* block, int* pid, int* fd);
+int purlin_vmm_multicast_join(PurlinVmmBlock* block, int pid, int fd);
+int purlin_vmm_multicast_bind(PurlinVmmBlock* block);
+uint64_t purlin_vmm_multicast_ptr(const PurlinVmmBlock* block);
+int purlin_vmm_detach(PurlinVmmBlock* block);
+int purlin_vmm_destroy(PurlinVmmBlock* block);
+
 #ifdef __cplusplus
 }
 #endif

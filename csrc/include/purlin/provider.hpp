@@ -8,7 +8,8 @@
 // provider; this build has no NVSHMEM dependency and ships:
 //   EmulatedMemory  world blocks on one GPU (single-GPU emulation, tests, fault modes)
 //   IpcMemory       CUDA IPC peer mappings; handles travel through a caller-supplied all-gather
-// The Python package adds the torch symmetric-memory provider (VMM + multicast).
+//   VmmMemory       CUDA virtual-memory blocks with POSIX-fd handles and an NVLS multicast alias (vmm_provider.cu)
+// The Python package adds the torch symmetric-memory provider.
 #pragma once
 #include <cuda_runtime.h>
 
@@ -18,6 +19,7 @@
 #include <string>
 #include <vector>
 
+#include "capi.h"
 #include "constants.hpp"
 
 namespace purlin {
@@ -120,6 +122,76 @@ class IpcMemory {
   AllGather ag_;
   Barrier barrier_;
   void* local_ = nullptr;
+};
+
+// One rank per GPU: separate processes, or the threads of one process. Memory comes from cuMemCreate, peers are
+// mapped from exported descriptors, and when every rank's device supports it all blocks are bound to one multicast
+// object whose mapping is returned as the NVLS alias. `allGather` and `barrier` as for IpcMemory.
+class VmmMemory {
+ public:
+  using AllGather = std::function<void(const void* send, void* recv, size_t bytesPerRank)>;
+  using Barrier = std::function<void()>;
+  VmmMemory(int rank, int world, int device, AllGather ag, Barrier barrier, bool wantMulticast = true)
+      : rank_(rank), world_(world), device_(device), ag_(std::move(ag)), barrier_(std::move(barrier)), wantMulticast_(wantMulticast) {}
+  SymmetricAllocation allocate_zeroed(size_t bytes, size_t /*alignment*/, cudaStream_t /*stream*/) {
+    block_ = purlin_vmm_create(device_, bytes, rank_, world_);
+    // every rank reports success or failure before anyone proceeds, so that a failure surfaces everywhere
+    struct Hello { int pid, fd, ok, multicast; } mine{0, -1, block_ ? 1 : 0, 0};
+    if (block_) {
+      purlin_vmm_local_handle(block_, &mine.pid, &mine.fd);
+      mine.multicast = wantMulticast_ && world_ > 1 && purlin_vmm_multicast_supported(device_) == 1 ? 1 : 0;
+    }
+    std::vector<Hello> all(static_cast<size_t>(world_));
+    ag_(&mine, all.data(), sizeof(Hello));
+    bool ok = true, multicast = true;
+    for (const Hello& h : all) { ok = ok && h.ok; multicast = multicast && h.multicast; }
+    if (!ok) { release(); throw std::runtime_error(std::string("VmmMemory: allocation failed on some rank: ") + purlin_last_error()); }
+    std::vector<int> pids, fds;
+    for (const Hello& h : all) { pids.push_back(h.pid); fds.push_back(h.fd); }
+    int good = purlin_vmm_map_peers(block_, pids.data(), fds.data()) == 0 ? 1 : 0;
+    if (!agree(good)) { release(); throw std::runtime_error(std::string("VmmMemory: peer mapping failed on some rank: ") + purlin_last_error()); }
+    if (multicast) {
+      int handle[2] = {0, -1};
+      int made = 1;
+      if (rank_ == 0) made = purlin_vmm_multicast_create(block_, &handle[0], &handle[1]) == 0 ? 1 : 0;
+      std::vector<int> handles(static_cast<size_t>(world_) * 2);
+      ag_(handle, handles.data(), sizeof(handle));
+      multicast = agree(made);                       // no object: carry on without the alias
+      if (multicast) {
+        good = purlin_vmm_multicast_join(block_, handles[0], handles[1]) == 0 ? 1 : 0;
+        if (!agree(good)) { release(); throw std::runtime_error(std::string("VmmMemory: joining the multicast object failed: ") + purlin_last_error()); }
+        good = purlin_vmm_multicast_bind(block_) == 0 ? 1 : 0;
+        if (!agree(good)) { release(); throw std::runtime_error(std::string("VmmMemory: binding the multicast object failed: ") + purlin_last_error()); }
+      }
+    }
+    barrier_();
+    SymmetricAllocation a;
+    for (int q = 0; q < world_; ++q) a.peers.push_back(reinterpret_cast<void*>(purlin_vmm_peer_ptr(block_, q)));
+    a.multicast = reinterpret_cast<void*>(purlin_vmm_multicast_ptr(block_));
+    return a;
+  }
+  void free(SymmetricAllocation& a) {
+    barrier_();   // nobody still reads or writes this block
+    if (block_) purlin_vmm_detach(block_);
+    barrier_();   // every alias and peer mapping is gone before any block is released
+    release();
+    a.peers.clear();
+    a.multicast = nullptr;
+  }
+ private:
+  // true when every rank passed 1; doubles as a barrier
+  bool agree(int mine) {
+    std::vector<int> all(static_cast<size_t>(world_));
+    ag_(&mine, all.data(), sizeof(int));
+    for (int v : all) if (!v) return false;
+    return true;
+  }
+  void release() { if (block_) { purlin_vmm_destroy(block_); block_ = nullptr; } }
+  int rank_, world_, device_;
+  AllGather ag_;
+  Barrier barrier_;
+  bool wantMulticast_;
+  PurlinVmmBlock* block_ = nullptr;
 };
 
 }  // namespace purlin

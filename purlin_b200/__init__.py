@@ -157,6 +157,8 @@ def finalize(handle: ContextHandle, stream_ptr: Optional[int] = None) -> None:
         return
     if handle.cpu is None:
         handle.mod.purlin_context_destroy(handle.ctx, _stream(stream_ptr))
+    if hasattr(handle.buf, "close"):
+        handle.buf.close()   # native providers release their mappings here (the vmm provider does so collectively)
     handle.ctx = None
     handle.cpu = None
     handle.hdl = None

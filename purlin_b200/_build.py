@@ -30,7 +30,7 @@ LIB_DIR = Path(__file__).resolve().parent / "_lib"
 ARCH = "100a"
 
 HOST_SOURCES = ["src/host_core.cpp", "src/split_policy.cpp"]
-CUDA_SOURCES = ["src/collectives.cu", "src/provider.cu", "src/gemm_sm100.cu", "src/fused_tp.cu", "src/moe.cu", "src/no_alloc.cu", "src/symm_ops.cu"]
+CUDA_SOURCES = ["src/collectives.cu", "src/provider.cu", "src/gemm_sm100.cu", "src/moe.cu", "src/no_alloc.cu", "src/symm_ops.cu", "src/vmm_provider.cu"]
 
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-lineinfo", "--expt-relaxed-constexpr",

@@ -2,10 +2,12 @@
 
 The reference abstracts this as the ``SymmetricMemoryProvider`` concept with an
 NVSHMEM implementation for C++ (csrc/contrib/symm_mem.cuh:10-59) and torch
-symmetric memory for Python (purlin/__init__.py:73-85).  Three providers exist here:
+symmetric memory for Python (purlin/__init__.py:73-85).  Four providers exist here:
 
 ``torch``     ``torch.distributed._symmetric_memory`` (CUDA VMM + NVLS multicast alias when the fabric offers it)
 ``ipc``       the native CUDA-IPC provider of libpurlin (peer mappings only, no multicast); handles travel over the process group
+``vmm``       the native virtual-memory provider of libpurlin (cuMemCreate blocks, POSIX-fd handles duplicated between the
+              ranks' processes, NVLS multicast alias when every device supports it); needs no torch symmetric memory
 ``emulated``  ``world`` blocks on one GPU, for single-GPU emulation of a multi-rank collective
 
 All return ``(owner, handle, peer_pointers, multicast_pointer)`` where ``owner`` keeps the memory alive.
@@ -25,6 +27,8 @@ def allocate_symmetric(nbytes: int, device: torch.device, group=None, provider: 
         return _torch_provider(nbytes, device, group)
     if provider == "ipc":
         return _ipc_provider(nbytes, device, group)
+    if provider == "vmm":
+        return _vmm_provider(nbytes, device, group)
     raise ValueError(f"unknown symmetric memory provider {provider!r}")
 
 
@@ -101,6 +105,101 @@ def _ipc_provider(nbytes: int, device: torch.device, group):
     dist.barrier(group)
     mapping = _IpcMapping(lib, local, opened)
     return mapping, mapping, peer_ptrs, 0
+
+
+class _VmmMapping:
+    """Owns a native virtual-memory block; releases it collectively (barrier, detach, barrier, destroy)."""
+
+    def __init__(self, lib, block, group):
+        self.lib, self.block, self.group = lib, block, group
+
+    def close(self):
+        import torch.distributed as dist
+        if not self.block:
+            return
+        collective = dist.is_initialized()
+        if collective:
+            dist.barrier(self.group)
+        self.lib.purlin_vmm_detach(C.c_void_p(self.block))
+        if collective:
+            dist.barrier(self.group)
+        self.lib.purlin_vmm_destroy(C.c_void_p(self.block))
+        self.block = None
+
+    def __del__(self):
+        # a collective release cannot run from a finaliser; drop the local mappings only
+        try:
+            if self.block:
+                self.lib.purlin_vmm_destroy(C.c_void_p(self.block))
+                self.block = None
+        except Exception:
+            pass
+
+
+def _vmm_provider(nbytes: int, device: torch.device, group):
+    import torch.distributed as dist
+    from .. import _native
+    lib = _native.cuda()
+    lib.purlin_vmm_create.restype = C.c_void_p
+    lib.purlin_vmm_create.argtypes = [C.c_int, C.c_size_t, C.c_int, C.c_int]
+    lib.purlin_vmm_local_handle.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.purlin_vmm_map_peers.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.purlin_vmm_peer_ptr.restype = C.c_uint64
+    lib.purlin_vmm_peer_ptr.argtypes = [C.c_void_p, C.c_int]
+    lib.purlin_vmm_multicast_create.argtypes = [C.c_void_p, C.POINTER(C.c_int), C.POINTER(C.c_int)]
+    lib.purlin_vmm_multicast_join.argtypes = [C.c_void_p, C.c_int, C.c_int]
+    lib.purlin_vmm_multicast_bind.argtypes = [C.c_void_p]
+    lib.purlin_vmm_multicast_ptr.restype = C.c_uint64
+    lib.purlin_vmm_multicast_ptr.argtypes = [C.c_void_p]
+    lib.purlin_vmm_detach.argtypes = [C.c_void_p]
+    lib.purlin_vmm_destroy.argtypes = [C.c_void_p]
+    lib.purlin_vmm_multicast_supported.argtypes = [C.c_int]
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    index = device.index if device.index is not None else torch.cuda.current_device()
+
+    def everyone(value):
+        got = [None] * world
+        dist.all_gather_object(got, value, group=group)
+        return got
+
+    block = lib.purlin_vmm_create(index, nbytes, rank, world)
+    pid, fd = C.c_int(0), C.c_int(-1)
+    if block:
+        lib.purlin_vmm_local_handle(C.c_void_p(block), C.byref(pid), C.byref(fd))
+    want_mc = bool(block) and world > 1 and not os.environ.get("PURLIN_DISABLE_MULTIMEM") and lib.purlin_vmm_multicast_supported(index) == 1
+    hello = everyone((bool(block), pid.value, fd.value, want_mc))
+    mapping = _VmmMapping(lib, block, group)
+
+    def give_up(what):
+        err = _native.last_error(lib)
+        if mapping.block:
+            lib.purlin_vmm_destroy(C.c_void_p(mapping.block))
+            mapping.block = None
+        raise RuntimeError(f"purlin: {what}: {err}")
+
+    if not all(h[0] for h in hello):
+        give_up("symmetric allocation failed on some rank")
+    pids = (C.c_int * world)(*[h[1] for h in hello])
+    fds = (C.c_int * world)(*[h[2] for h in hello])
+    ok = lib.purlin_vmm_map_peers(C.c_void_p(block), pids, fds) == 0
+    if not all(everyone(ok)):
+        give_up("mapping the peers' blocks failed on some rank")
+    if all(h[3] for h in hello):
+        mpid, mfd, made = C.c_int(0), C.c_int(-1), True
+        if rank == 0:
+            made = lib.purlin_vmm_multicast_create(C.c_void_p(block), C.byref(mpid), C.byref(mfd)) == 0
+        first = everyone((made, mpid.value, mfd.value))[0]
+        if first[0]:   # without a multicast object the block simply has no alias
+            ok = lib.purlin_vmm_multicast_join(C.c_void_p(block), first[1], first[2]) == 0
+            if not all(everyone(ok)):
+                give_up("joining the multicast object failed on some rank")
+            ok = lib.purlin_vmm_multicast_bind(C.c_void_p(block)) == 0
+            if not all(everyone(ok)):
+                give_up("binding the multicast object failed on some rank")
+    dist.barrier(group)
+    peer_ptrs = [int(lib.purlin_vmm_peer_ptr(C.c_void_p(block), q)) for q in range(world)]
+    mc = int(lib.purlin_vmm_multicast_ptr(C.c_void_p(block)))
+    return mapping, mapping, peer_ptrs, mc
 
 
 def allocate_emulated(nbytes: int, world: int, device: torch.device) -> Tuple[list, list]:

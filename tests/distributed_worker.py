@@ -84,8 +84,9 @@ def main():
 
     mc = h.has_multicast
     if rank == 0:
-        print(f"world {world} multicast {mc} staging {staging}", flush=True)
+        print(f"world {world} multicast {mc} staging {staging} provider {os.environ.get('PURLIN_PROVIDER', 'torch')}", flush=True)
     W = world
+    subset = bool(os.environ.get("PURLIN_TEST_SUBSET"))   # second pass with another provider: defaults, NVLS and V cases only
     # all-reduce: every band, forced
     ar_cases = [("one-shot packets", dict(regime=0, arPath=0, lrBlocks=8), 32 * W * 8),
                 ("two-shot packets", dict(regime=0, arPath=1, lrBlocks=8), 32 * W * 64),
@@ -93,7 +94,7 @@ def main():
                 ("staged composed", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8), 1 << 20),
                 ("staged composed chunked", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=256 << 10), 3 << 20),
                 ("segmented", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=1 << 20), staging * 2 + W * 32 * 8)]
-    for name, kw, n in ar_cases:
+    for name, kw, n in ([] if subset else ar_cases):
         for dtype in (0, 4, 1):
             case(f"AR {name} dt{dtype}", AR, nbytes=n, dtype=dtype, pol=policy(**kw))
         case(f"AR {name} max", AR, nbytes=n, dtype=0, op=2, pol=policy(**kw))
@@ -107,7 +108,7 @@ def main():
                 case(f"AR {name} dt{dtype}", AR, nbytes=n, dtype=dtype, pol=policy(**kw))
             case(f"AR {name} max", AR, nbytes=n, dtype=0, op=2, pol=policy(**kw))
         case("RS nvls", RS, nbytes=1 << 18, dtype=0, pol=policy(memType=1, consumeBlocks=16, putBlocks=8))
-    for coll, cname in ((AG, "AG"), (RS, "RS"), (A2A, "A2A")):
+    for coll, cname in (() if subset else ((AG, "AG"), (RS, "RS"), (A2A, "A2A"))):
         for name, kw, n in (("packets", dict(regime=0, lrBlocks=8), 32 * 40), ("staged", dict(), 1 << 19),
                             ("chunked", dict(chunkBytes=128 << 10), (1 << 20) + 64), ("cyclic", dict(chunkBytes=256 << 10), staging // 2)):
             case(f"{cname} {name}", coll, nbytes=n, dtype=0, pol=policy(putBlocks=max(8, W), consumeBlocks=max(16, 2 * W), **kw))

@@ -19,3 +19,23 @@ def test_cpp_binary(name):
     print(res.stdout[-4000:])
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
     assert "PASSED" in res.stdout
+
+
+@pytest.mark.multigpu
+@pytest.mark.parametrize("args", [
+    ["all", "8K", "4M", "0", "3", "1", "--provider", "vmm", "--staging", "8M"],
+    ["all", "32K", "2M", "2", "3", "1", "--provider", "peer", "--staging", "8M", "--reduction-mode", "deterministic"],
+    ["ar", "16M", "32M", "0", "3", "1", "--provider", "vmm", "--staging", "8M"],     # payload larger than the staging buffer
+], ids=["vmm-stream", "peer-graph-deterministic", "vmm-segmented"])
+def test_multi_gpu_bench_binary(args):
+    """One process, one thread per GPU, all seven collectives through purlin::initialize / allReduce / ... / finalize
+    with the native virtual-memory provider (NVLS alias included) or plain peer memory; every size compared exactly."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    from purlin_b200 import _build
+    exe = [e for e in _build.build_cpp_tests() if e.name == "multi_gpu_bench"][0]
+    res = subprocess.run([str(exe), *args], capture_output=True, text=True, timeout=600)
+    print(res.stdout[-6000:])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
+    assert "PASSED" in res.stdout

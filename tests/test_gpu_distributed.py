@@ -13,11 +13,15 @@ import torch
 pytestmark = [pytest.mark.gpu, pytest.mark.multigpu]
 
 
-def test_all_collectives_all_gpus():
+@pytest.mark.parametrize("provider", ["torch", "vmm", "ipc"])
+def test_all_collectives_all_gpus(provider):
     n = torch.cuda.device_count()
     n = 8 if n >= 8 else 4 if n >= 4 else 2
     here = os.path.dirname(os.path.abspath(__file__))
     env = dict(os.environ)
+    env["PURLIN_PROVIDER"] = provider
+    if provider != "torch":
+        env["PURLIN_TEST_SUBSET"] = "1"   # the protocol bands were covered by the first pass; this one is about the memory
     env.setdefault("NCCL_NVLS_ENABLE", "0")   # NCCL only bootstraps here; keep its multicast objects out of the picture
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", "29581", os.path.join(here, "distributed_worker.py")]

@@ -130,3 +130,18 @@ def test_initialize_asks_for_the_reference_workspace_and_forwards_multicast(monk
     assert c["create"] and c["rank"] == 1 and c["world"] == world and c["mc"] == 0xABC000 and c["stream"] == 1234
     assert c["ptrs"] == [0x1000 * (q + 1) for q in range(world)] and c["staging"] == purlin.STAGING_BUFFER_SIZE
     assert h.ctx == 0xC0FFEE and h.buf == "buf" and h.has_multicast
+
+
+def test_vmm_provider_fails_cleanly_without_a_driver():
+    """On a machine without a CUDA driver the native virtual-memory provider reports an error instead of crashing."""
+    import ctypes as C
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("this check is about machines without a GPU")
+    from purlin_b200 import _native
+    lib = _native.cuda()
+    lib.purlin_vmm_create.restype = C.c_void_p
+    lib.purlin_vmm_create.argtypes = [C.c_int, C.c_size_t, C.c_int, C.c_int]
+    assert not lib.purlin_vmm_create(0, 1 << 20, 0, 2)
+    assert "vmm provider" in _native.last_error(lib)
+    assert lib.purlin_vmm_multicast_supported(0) == -1
