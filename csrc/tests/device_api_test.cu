@@ -13,6 +13,8 @@
 #include "purlin/capi.h"
 #include "purlin/collective.cuh"
 #include "purlin/layout.hpp"
+#include "purlin/pipeline.hpp"
+#include "purlin/static_for.hpp"
 
 using namespace purlin;
 
@@ -56,6 +58,46 @@ __global__ void __launch_bounds__(256, 1) scaleThenAllReduce(const RankArgs* ran
 // the Atom on its own: one CTA copies a slice, src or dst may be peer memory
 __global__ void atomCopy(unsigned char* dst, const unsigned char* src, size_t bytes) {
   superCopy<DefaultAtom>(dst, src, bytes, blockIdx.x, gridDim.x);
+}
+
+// the prefetch-ring driver with a real asynchronous operation: every thread keeps Depth cp.async copies of 16 bytes
+// in flight through its own column of a shared-memory ring (no CTA barrier needed: a thread reads only what it loaded)
+template <int Depth, int Threads>
+struct CpAsyncCopy {
+  const uint4* src;
+  uint4* dst;
+  size_t vecs;
+  uint4* ring;   // Depth x Threads vectors of shared memory
+  __device__ void prepare() {}
+  __device__ void prefetch(int slot, size_t stage) {
+    const size_t i = stage * Threads + threadIdx.x;
+    if (i < vecs) {
+      const unsigned smem = unsigned(__cvta_generic_to_shared(ring + slot * Threads + threadIdx.x));
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem), "l"(src + i) : "memory");
+    }
+  }
+  __device__ void commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+  template <int N> __device__ void wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+  __device__ void consume(int slot, size_t stage) {
+    const size_t i = stage * Threads + threadIdx.x;
+    if (i < vecs) dst[i] = ring[slot * Threads + threadIdx.x];
+  }
+  __device__ void advance() {}
+};
+
+__global__ void __launch_bounds__(256) pipelinedCopy(const uint4* src, uint4* dst, size_t vecs, int* loopSum) {
+  constexpr int kDepth = 4, kThreads = 256;
+  __shared__ uint4 ring[kDepth * kThreads];
+  const size_t per = (vecs + gridDim.x - 1) / gridDim.x;
+  const size_t begin = size_t(blockIdx.x) * per;
+  const size_t mine = begin >= vecs ? 0 : (vecs - begin < per ? vecs - begin : per);
+  CpAsyncCopy<kDepth, kThreads> op{src + begin, dst + begin, mine, ring};
+  Pipeline<kDepth>::run(op, (mine + kThreads - 1) / kThreads);
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    int t = 0;
+    staticFor<5>([&](auto i) { t += decltype(i)::value * decltype(i)::value; });   // 0 + 1 + 4 + 9 + 16
+    *loopSum = t;
+  }
 }
 
 int main() {
@@ -123,6 +165,29 @@ int main() {
   for (unsigned char b : got) same = same && b == 0x5a;
   std::printf("%s  user kernel: Atom superCopy over a peer pointer\n", same ? "ok  " : "FAIL");
   if (!same) ++failures;
+
+  // the compile-time loop and the prefetch ring inside a kernel (cp.async as the asynchronous operation)
+  {
+    const size_t vecs = 65539;   // not a multiple of the CTA size, nor of the grid
+    std::vector<uint32_t> pattern(vecs * 4), back(vecs * 4, 0);
+    for (size_t i = 0; i < pattern.size(); ++i) pattern[i] = uint32_t(i * 2654435761u + 12345u);
+    uint4 *dSrc, *dDst;
+    int* dSum;
+    cudaMalloc(&dSrc, vecs * 16); cudaMalloc(&dDst, vecs * 16); cudaMalloc(&dSum, sizeof(int));
+    cudaMemcpy(dSrc, pattern.data(), vecs * 16, cudaMemcpyHostToDevice);
+    cudaMemset(dDst, 0, vecs * 16);
+    pipelinedCopy<<<7, 256, 0, stream>>>(dSrc, dDst, vecs, dSum);
+    int loopSum = 0;
+    cudaMemcpyAsync(back.data(), dDst, vecs * 16, cudaMemcpyDeviceToHost, stream);
+    cudaMemcpyAsync(&loopSum, dSum, sizeof(int), cudaMemcpyDeviceToHost, stream);
+    const cudaError_t pe = cudaStreamSynchronize(stream);
+    const bool copied = pe == cudaSuccess && back == pattern;
+    std::printf("%s  user kernel: Pipeline<4> over cp.async copies %zu vectors exactly\n", copied ? "ok  " : "FAIL", vecs);
+    std::printf("%s  user kernel: staticFor in device code\n", loopSum == 30 ? "ok  " : "FAIL");
+    if (!copied) ++failures;
+    if (loopSum != 30) ++failures;
+    cudaFree(dSrc); cudaFree(dDst); cudaFree(dSum);
+  }
 
   for (int r = 0; r < W; ++r) purlin_context_destroy(ctxs[r], stream);
   std::printf("%s: %d failure(s)\n", failures ? "FAILED" : "PASSED", failures);

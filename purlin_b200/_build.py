@@ -179,8 +179,27 @@ def build_cpp_tests(force: bool = False, verbose: bool = False):
     return out
 
 
+def build_cpu_tests(force: bool = False, verbose: bool = False):
+    """Host-only C++ unit tests (csrc/tests/*.cpp): header-level checks that need neither nvcc nor a GPU."""
+    out = []
+    LIB_DIR.mkdir(parents=True, exist_ok=True)
+    for src in sorted((CSRC / "tests").glob("*.cpp")):
+        exe = LIB_DIR / src.stem
+        stamp = LIB_DIR / (src.stem + ".key")
+        key = cache_key(src.stem, [src], CXX_FLAGS)
+        if force or not exe.exists() or not stamp.exists() or stamp.read_text().strip() != key:
+            with BuildLock(LIB_DIR / ".build.lock"):
+                tmp = LIB_DIR / f".{src.stem}.{os.getpid()}.tmp"
+                _run(["g++", *CXX_FLAGS, "-I", str(CSRC / "include"), str(src), "-o", str(tmp)], verbose)
+                tmp.replace(exe)
+                stamp.write_text(key)
+        out.append(exe)
+    return out
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return build_host(force, verbose), build_cuda(force, verbose), *build_cpp_tests(force, verbose)
+    return (build_host(force, verbose), build_cuda(force, verbose), *build_cpp_tests(force, verbose),
+            *build_cpu_tests(force, verbose))
 
 
 if __name__ == "__main__":
