@@ -160,11 +160,11 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
         flags, force, verbose)
 
 
-def build_cpp_tests(force: bool = False, verbose: bool = False):
-    """The C++ host-API test binary (csrc/tests), linked against the in-tree libpurlin_cuda.so."""
+def build_cpp_tests(force: bool = False, verbose: bool = False, folder: str = "tests"):
+    """The C++ test binaries (csrc/tests) or example programs (csrc/examples), linked against the in-tree libpurlin_cuda.so."""
     lib = build_cuda(force, verbose)
     out = []
-    for src in sorted((CSRC / "tests").glob("*.cu")):
+    for src in sorted((CSRC / folder).glob("*.cu")):
         exe = LIB_DIR / src.stem
         stamp = LIB_DIR / (src.stem + ".key")
         key = cache_key(src.stem, [src, lib], NVCC_FLAGS)
@@ -197,9 +197,14 @@ def build_cpu_tests(force: bool = False, verbose: bool = False):
     return out
 
 
+def build_examples(force: bool = False, verbose: bool = False):
+    """The C++ example programs of csrc/examples (device-side collectives, copy-engine baselines, push/pull)."""
+    return build_cpp_tests(force, verbose, folder="examples")
+
+
 def build_all(force: bool = False, verbose: bool = False):
     return (build_host(force, verbose), build_cuda(force, verbose), *build_cpp_tests(force, verbose),
-            *build_cpu_tests(force, verbose))
+            *build_examples(force, verbose), *build_cpu_tests(force, verbose))
 
 
 if __name__ == "__main__":

@@ -139,6 +139,61 @@ def main():
     purlin.check(h)
     if not torch.all(out == W).item():
         failures.append("back-to-back all-reduce")
+    # a delayed rank: the last rank's stream is busy for a while before it joins; the others wait inside their bound
+    if rank == W - 1:
+        torch.cuda._sleep(200_000_000)      # about 0.1 s of device time, far below the 5 s limit of the waits
+    case("AR after a delayed rank", AR, nbytes=1 << 20, dtype=0, reps=1)
+    case("A2AV after a delayed rank", A2AV, sizes=mat, dtype=0, reps=1)
+    # skewed and hot-ring traffic (the split policies of the benchmark harness)
+    from purlin_b200.utils import split_policy as sp
+    for percent in (25, 50):
+        sk = sp.skew_splits(W * (96 << 10), W, percent, seed=percent)
+        case(f"AGV skew {percent}", AGV, sizes=sk, dtype=0, reps=1)
+        case(f"RSV skew {percent}", RSV, sizes=sk, dtype=0, reps=1)
+    case("A2AV hot ring", A2AV, sizes=sp.hot_ring_matrix(W, 256 << 10, 90), dtype=0, reps=1)
+    case("A2AV sparse", A2AV, sizes=sp.sparse_matrix(W, 1, 64 << 10, seed=5), dtype=0, reps=1)
+    case("A2AV self only", A2AV, sizes=[[(8 << 10) if r == q else 0 for q in range(W)] for r in range(W)], dtype=0, reps=1)
+    # one context, mixed collective kinds and grid sizes, 32 calls back to back without synchronisation, inputs changed
+    # on the device between calls (a stale read of an earlier call's staging would show), in a stream and from a graph
+    n = 32 * W * 16
+    src = torch.zeros(n, device=dev, dtype=torch.float32)
+    ar_out = torch.empty(n, device=dev, dtype=torch.float32)
+    ag_out = torch.empty(n * W, device=dev, dtype=torch.float32)
+    rs_out = torch.empty(n // W, device=dev, dtype=torch.float32)
+    aa_out = torch.empty(n, device=dev, dtype=torch.float32)
+
+    def mixed_round():
+        src.add_(1.0)                                     # the "device counter": data differ in every round
+        purlin.all_reduce(src, ar_out, h, None)
+        purlin.all_gather(src, ag_out, h, None)
+        purlin.reduce_scatter(src, rs_out, h, None)
+        purlin.all_to_all(src, aa_out, h, None)
+
+    for _ in range(8):
+        mixed_round()
+    purlin.check(h)
+    rounds = 8
+    gr = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(gr, stream=side):
+            for _ in range(8):
+                mixed_round()
+    for _ in range(4):
+        gr.replay()
+        rounds += 8
+    try:
+        purlin.check(h)
+        good = (torch.all(ar_out == rounds * W).item() and torch.all(ag_out == rounds).item()
+                and torch.all(rs_out == rounds * W).item() and torch.all(aa_out == rounds).item())
+        if not good:
+            failures.append(f"mixed back-to-back calls: expected round {rounds}, all-reduce saw {float(ar_out[0])}, all-gather {float(ag_out[0])}")
+        else:
+            count += 1
+    except TimeoutError as err:
+        failures.append(f"mixed back-to-back calls: {err}")
+        purlin.clear_status(h)
     # zero-copy all-reduce on a tensor allocated in symmetric memory (NVLS when offered, peer loads otherwise)
     for dtype, n in ((torch.bfloat16, 1 << 20), (torch.float32, 32 * W * 9)):
         st = purlin.symm_empty((n,), dtype, h)

@@ -39,3 +39,22 @@ def test_multi_gpu_bench_binary(args):
     print(res.stdout[-6000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert "PASSED" in res.stdout
+
+
+@pytest.mark.parametrize("name,args", [
+    ("device_collectives", ["ar", "262144", "24", "3"]),
+    ("device_collectives", ["ag", "262144", "24", "3"]),
+    ("device_collectives", ["rs", "262144", "24", "3"]),
+    ("device_collectives", ["a2a", "262144", "24", "3"]),
+    ("device_collectives", ["ar", "98304", "12", "2", "8"]),
+    ("copy_engine", ["4194304", "16", "3"]),
+], ids=["device-ar", "device-ag", "device-rs", "device-a2a", "device-ar-8-ranks", "copy-engine"])
+def test_cpp_example(name, args):
+    """The example programs of csrc/examples: user kernels calling the device-side collectives with hand-set launch
+    configurations (virtual ranks on one GPU), and the copy-engine / push / pull point-to-point comparison."""
+    from purlin_b200 import _build
+    exe = [e for e in _build.build_examples() if e.name == name][0]
+    res = subprocess.run([str(exe), *args], capture_output=True, text=True, timeout=300)
+    print(res.stdout[-3000:])
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "PASSED" in res.stdout
