@@ -100,14 +100,26 @@ int main(int argc, char** argv) {
   for (auto& b : blocks) { void* p = nullptr; cudaMalloc(&p, ws[6]); cudaMemset(p, 0, ws[6]); b = reinterpret_cast<uint64_t>(p); }
   std::vector<PurlinHostContext*> ctxs(static_cast<size_t>(W), nullptr);
   std::vector<RankArgs> host(static_cast<size_t>(W));
+  // The layout engine rounds role sizes (consumers per peer, gatherers per shard owner), so a plan can be wider than
+  // the sum asked for: shrink the request until every rank's row fits on the GPU at the same time.
   int gridX = 1;
+  for (int attempt = 0; attempt < 64; ++attempt) {
+    gridX = 1;
+    for (int r = 0; r < W; ++r) {
+      if (purlin_plan_build(int(type), W, r, bytes, nullptr, nullptr, int(DType::fp32), int(ReduceOp::add), 0, 0, 0, staging, &pol,
+                            &host[r].plan, nullptr) != 0) { std::printf("FAIL plan: %s\n", purlin_last_error()); return 1; }
+      gridX = std::max(gridX, int(host[r].plan.blocks));
+    }
+    if (gridX * W <= prop.multiProcessorCount) break;
+    if (pol.putBlocks > 1) --pol.putBlocks;
+    else if (pol.consumeBlocks > 1) --pol.consumeBlocks;
+    else if (pol.gatherBlocks > 1) --pol.gatherBlocks;
+    else break;
+  }
   for (int r = 0; r < W; ++r) {
     ctxs[r] = purlin_context_create(r, W, blocks.data(), 0, staging, 2000000000ull, stream);
     if (!ctxs[r]) { std::printf("FAIL context: %s\n", purlin_last_error()); return 1; }
     host[r].ctx = *static_cast<const Context*>(purlin_context_device_struct(ctxs[r]));
-    if (purlin_plan_build(int(type), W, r, bytes, nullptr, nullptr, int(DType::fp32), int(ReduceOp::add), 0, 0, 0, staging, &pol,
-                          &host[r].plan, nullptr) != 0) { std::printf("FAIL plan: %s\n", purlin_last_error()); return 1; }
-    gridX = std::max(gridX, int(host[r].plan.blocks));
     std::vector<float> in(inElems);
     for (size_t i = 0; i < inElems; ++i) in[i] = valueAt(r, i);
     float *dIn = nullptr, *dOut = nullptr;
