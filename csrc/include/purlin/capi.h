@@ -29,6 +29,8 @@ int purlin_workspace_layout(int world, size_t stagingTRSize, size_t* ws);
 int purlin_plan_build(int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
                       int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace, size_t stagingTRSize,
                       const void* policy, void* planOut, void* policyOut);
+/* Static bounds check of a plan against one rank's buffer extents (every plan the library builds has passed it). */
+int purlin_plan_check(const void* plan, int world, size_t stagingTRSize, size_t srcBytes, size_t dstBytes);
 int purlin_default_policy(int collective, int world, size_t bytes, int dtype, int mode, int multicastAvailable,
                           size_t stagingTRSize, void* policyOut);
 int purlin_topology(int inLayout, int outLayout, int op, int cyclic, int* out8);

@@ -15,6 +15,7 @@
 #include <mutex>
 #include <string>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 #include "purlin/capi.h"
@@ -159,14 +160,17 @@ int worldOneCopy(const CollectiveSpec& s, const void* src, void* dst, cudaStream
   return 0;
 }
 
-// kernels that stream through the bulk ring need more dynamic shared memory than the default limit: opt in once each
+// kernels that stream through the bulk ring need more dynamic shared memory than the default limit: opt in once per
+// (device, kernel) pair, since the attribute belongs to the device's copy of the function
 bool ensureSmemOptIn(const void* fn) {
   static std::mutex mu;
-  static std::vector<const void*> done;
+  static std::vector<std::pair<int, const void*>> done;
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess) return false;
   std::lock_guard<std::mutex> g(mu);
-  for (const void* f : done) if (f == fn) return true;
+  for (const auto& d : done) if (d.first == device && d.second == fn) return true;
   if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bulk::smemBytes(bulk::kMaxDepth))) != cudaSuccess) return false;
-  done.push_back(fn);
+  done.emplace_back(device, fn);
   return true;
 }
 

@@ -616,9 +616,15 @@ template <int EPI, int COMM, int CTAS>
 int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
   auto kernel = gemmKernel<EPI, COMM, CTAS>;
   constexpr int threads = COMM == kCommAG ? kThreadsComm : kThreadsPlain;
-  static int maxClusters = -1;
-  if (maxClusters < 0) {
+  // shared-memory opt-in and cluster occupancy belong to the device's copy of the kernel: resolve them once per device
+  static int perDevice[64];
+  static bool seen[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) { setError("GEMM launch: no current device"); return 1; }
+  int& maxClusters = perDevice[device];
+  if (!seen[device]) {
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit) != cudaSuccess) { setError("cannot opt in to 227 KiB of shared memory"); return 1; }
+    seen[device] = true;
     maxClusters = smCount() / CTAS;
     if (CTAS == 2) {
       // pairs must sit on SMs of one GPC: ask how many pairs the device can hold at once

@@ -17,6 +17,7 @@
 
 #include "purlin/capi.h"
 #include "purlin/layout.hpp"
+#include "purlin/plan_check.hpp"
 #include "purlin/tuning.hpp"
 
 namespace purlin {
@@ -58,17 +59,25 @@ bool makeSpec(CollectiveSpec& s, int collective, int world, int rank, size_t byt
               int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace) {
   return fillSpec(s, collective, world, rank, bytes, sizes, outSizes, dtype, reduceOp, mode, multicastAvailable, inPlace);
 }
+// build, then bounds-check: no plan leaves this function unchecked
+static bool buildChecked(const CollectiveSpec& s, const Policy& p, const WorkspaceLayout& ws, Plan& plan, std::string& err) {
+  if (!buildPlan(s, p, ws, plan, err)) return false;
+  const std::string violation = checkPlan(plan, s.world, ws, extentsFor(s));
+  if (!violation.empty()) { err = "plan check: " + violation; return false; }
+  return true;
+}
+
 bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen) {
   std::string err;
   Policy p = forced ? *forced : selectPolicy(s, ws);
-  bool ok = buildPlan(s, p, ws, plan, err);
+  bool ok = buildChecked(s, p, ws, plan, err);
   if (!ok && !forced) {   // a measured band may not fit this call (uneven V sizes): fall back to built-in choices
     std::string err2;
     p = defaultPolicy(s, ws);
-    ok = buildPlan(s, p, ws, plan, err2);
+    ok = buildChecked(s, p, ws, plan, err2);
     if (!ok && p.regime == int32_t(Regime::latency)) {
       p.regime = int32_t(Regime::throughput);
-      ok = buildPlan(s, p, ws, plan, err2);
+      ok = buildChecked(s, p, ws, plan, err2);
     }
     if (!ok) err = err2;
   }
@@ -102,6 +111,18 @@ int purlin_plan_build(int collective, int world, int rank, size_t bytes, const s
   Plan plan;
   if (!planFor(s, ws, static_cast<const Policy*>(policy), plan, static_cast<Policy*>(policyOut))) return 1;
   std::memcpy(planOut, &plan, sizeof(plan));
+  return 0;
+}
+
+// Bounds check of a plan against one rank's buffer extents; 0 when sound, 1 (and purlin_last_error) when not.
+int purlin_plan_check(const void* planIn, int world, size_t stagingTRSize, size_t srcBytes, size_t dstBytes) {
+  if (!planIn || world < 1 || world > kMaxRanks) { setError("plan check: invalid arguments"); return 1; }
+  Plan plan;
+  std::memcpy(&plan, planIn, sizeof(plan));
+  PlanExtents e;
+  e.srcBytes = srcBytes; e.dstBytes = dstBytes;
+  const std::string violation = checkPlan(plan, world, workspaceLayout(world, stagingTRSize), e);
+  if (!violation.empty()) { setError("plan check: " + violation); return 1; }
   return 0;
 }
 

@@ -277,6 +277,15 @@ def build_plan(collective, world, rank, nbytes=0, sizes=None, out_sizes=None, dt
     return plan, chosen
 
 
+def check_plan(plan, world, src_bytes, dst_bytes, staging_size=STAGING_BUFFER_SIZE) -> str:
+    """Static bounds check of a plan against one rank's buffer extents. Returns "" when sound, else the first violation
+    (every plan ``build_plan`` or a collective call produces has already passed this check)."""
+    lib = _native.host()
+    lib.purlin_plan_check.argtypes = [C.c_void_p, C.c_int, C.c_size_t, C.c_size_t, C.c_size_t]
+    rc = lib.purlin_plan_check(C.byref(plan), world, staging_size, src_bytes, dst_bytes)
+    return "" if rc == 0 else _native.last_error(lib)
+
+
 Policy = _native.Policy
 
 

@@ -1,0 +1,108 @@
+"""The static bounds check every plan passes before it can be launched or interpreted.
+
+Stands in for the sanitizer runs the reference does not have either (its correctness rests on static_asserts inside
+the templates, e.g. csrc/include/purlin/snac.cuh:55-56): worlds 2-16, every collective, sizes around the boundaries
+where the policy changes protocol (packets / resident / chunked / cyclic / segmented), forced policies, and plans
+corrupted on purpose.
+"""
+import copy
+
+import pytest
+
+import purlin_b200 as P
+from helpers import AR, AG, AGV, RS, RSV, A2A, A2AV, in_out_bytes, policy
+
+STAGING = 1 << 20
+
+
+def _sizes_for(coll, world, unit):
+    if coll in (AGV, RSV):
+        return [unit * ((q * 7) % 5) for q in range(world)], None
+    if coll == A2AV:
+        mat = [[unit * ((r * 3 + q * 5) % 4) for q in range(world)] for r in range(world)]
+        return mat, None
+    return None, None
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 5, 8, 12, 16])
+@pytest.mark.parametrize("coll", [AR, AG, RS, A2A])
+def test_fixed_size_plans_pass_around_every_boundary(world, coll):
+    unit = 32 * world
+    # band boundaries of the built-in policy are powers of two between 1 KiB and the staging size; probe one unit either side
+    probes = set()
+    for shift in range(10, 23):
+        for d in (-unit, 0, unit):
+            n = ((1 << shift) + d) // unit * unit
+            if n >= unit:
+                probes.add(n)
+    probes.update({unit, 2 * unit, STAGING // world // unit * unit, STAGING, STAGING + unit, 3 * STAGING})
+    checked = 0
+    for n in sorted(probes):
+        for rank in {0, world - 1}:
+            try:
+                plan, _ = P.build_plan(coll, world, rank, n, dtype=P.DataType.BF16, staging_size=STAGING)
+            except RuntimeError as e:
+                assert "plan check" not in str(e), f"coll {coll} world {world} bytes {n}: {e}"
+                continue   # a size the engine refuses outright (e.g. beyond what the staging buffer can stream)
+            ib, ob = in_out_bytes(coll, world, rank, n, None)
+            assert P.check_plan(plan, world, ib, ob, STAGING) == ""
+            checked += 1
+    assert checked > 20
+
+
+@pytest.mark.parametrize("world", [2, 4, 7, 16])
+@pytest.mark.parametrize("coll", [AGV, RSV, A2AV])
+def test_variable_length_plans_pass(world, coll):
+    for unit in (32, 4096, 96 << 10):
+        sizes, _ = _sizes_for(coll, world, unit)
+        for rank in range(world):
+            if coll == A2AV:
+                ins, outs = sizes[rank], [sizes[q][rank] for q in range(world)]
+                plan, _ = P.build_plan(coll, world, rank, 0, sizes=ins, out_sizes=outs, staging_size=STAGING)
+            else:
+                plan, _ = P.build_plan(coll, world, rank, 0, sizes=sizes, staging_size=STAGING)
+            ib, ob = in_out_bytes(coll, world, rank, 0, sizes)
+            assert P.check_plan(plan, world, ib, ob, STAGING) == ""
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(chunkBytes=32768), dict(regime=0), dict(arPath=0), dict(regime=0, arPath=0),
+                                dict(chunkBytes=65536, arPath=1)])
+def test_forced_policies_pass(kw):
+    for world in (2, 4, 8):
+        for coll in (AR, AG, RS, A2A):
+            n = 32 * world * 96
+            plan, _ = P.build_plan(coll, world, 1, n, staging_size=STAGING, policy=policy(**kw))
+            ib, ob = in_out_bytes(coll, world, 1, n, None)
+            assert P.check_plan(plan, world, ib, ob, STAGING) == ""
+
+
+def test_corrupted_plans_are_caught():
+    world, n = 4, 32 * 4 * 512
+    plan, _ = P.build_plan(AG, world, 0, n, staging_size=STAGING, policy=policy(chunkBytes=16384))
+    ib, ob = in_out_bytes(AG, world, 0, n, None)
+    assert P.check_plan(plan, world, ib, ob, STAGING) == ""
+    assert "source" in P.check_plan(plan, world, ib - 32, ob, STAGING)            # the caller's buffer is shorter than claimed
+    assert "destination" in P.check_plan(plan, world, ib, ob - 32, STAGING)
+
+    def mutated(fn):
+        p = copy.deepcopy(plan)
+        fn(p)
+        return P.check_plan(p, world, ib, ob, STAGING)
+
+    stage = next(i for i in range(plan.nSteps) if plan.steps[i].role == 0)
+    consume = next(i for i in range(plan.nSteps) if plan.steps[i].role == 2)
+    assert "staging window" in mutated(lambda p: setattr(p.steps[stage], "dstOff", STAGING - 64))
+    assert "staging window" in mutated(lambda p: setattr(p.steps[consume], "srcOff", STAGING))
+    assert "CTA range" in mutated(lambda p: setattr(p.steps[consume], "blockBegin", p.blocks))
+    assert "chunks" in mutated(lambda p: setattr(p.steps[stage], "chunks", p.steps[stage].chunks + 1))
+    assert "aligned" in mutated(lambda p: setattr(p.steps[consume], "dstOff", p.steps[consume].dstOff + 8))
+    assert "peer" in mutated(lambda p: setattr(p.steps[consume], "peer", world))
+    assert "grid size" in mutated(lambda p: setattr(p, "blocks", 0))
+    # packets: an all-reduce small enough for the latency regime
+    small, _ = P.build_plan(AR, world, 0, 32 * world * 4, staging_size=STAGING, policy=policy(regime=0, arPath=1, lrBlocks=2))
+    nb = 32 * world * 4
+    assert P.check_plan(small, world, nb, nb, STAGING) == ""
+    put = next(i for i in range(small.nSteps) if small.steps[i].role >= 5)
+    bad = copy.deepcopy(small)
+    bad.steps[put].dstOff = 8 << 20
+    assert "packet slot" in P.check_plan(bad, world, nb, nb, STAGING)
