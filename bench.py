@@ -19,7 +19,6 @@ import argparse
 import json
 import os
 import sys
-import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
@@ -153,8 +152,9 @@ def main():
     mlp.tp.check()
 
     # ---- device-timed region: exactly `steps` steps, one event pair per rank, max over ranks ----
+    clocks = ClockSampler(local)   # NVML is brought up here, outside the timed region
     barrier()
-    with ClockSampler(local) as clocks:
+    with clocks:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(args.steps):
@@ -180,11 +180,15 @@ def main():
     for _ in range(3):
         e2e_step()
     barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
-    barrier()
-    e2e_ms = (time.perf_counter() - t0) * 1e3
+    with clocks:   # same sampler: the clock record covers both timed regions
+        ea, eb = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ea.record()
+        for _ in range(args.steps):
+            e2e_step()
+        eb.record()
+        eb.synchronize()
+        barrier()
+    e2e_ms = ea.elapsed_time(eb)   # device time from before the first copy to after the last read, host gaps included
     te = torch.tensor([e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(te, op=dist.ReduceOp.MAX)

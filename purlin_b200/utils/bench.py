@@ -116,45 +116,79 @@ def parse_size(s: str) -> int:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML while a timed region runs (read-only)."""
+    """Samples SM clocks and throttle reasons through NVML while a timed region runs (read-only).
 
-    def __init__(self, index: int = 0, period_s: float = 0.005):
+    NVML is initialised in the constructor, outside the timed region, so the sampling thread spends the region
+    sampling. One sampler can bracket several regions (``with sampler: ...`` more than once); samples accumulate.
+    """
+
+    def __init__(self, index: int = 0, period_s: float = 0.001):
         import threading
         self.index, self.period = index, period_s
         self.samples, self.reasons = [], set()
         self.max_mhz = 0
+        self._threading = threading
         self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
+        self._thread = None
+        self._nvml = self._handle = None
+        self._names = {}
         try:
             import pynvml
             pynvml.nvmlInit()
-            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
-            names = {
+            self._nvml = pynvml
+            self._handle = self._handle_for(pynvml, self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._names = {
                 pynvml.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
                 pynvml.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
                 pynvml.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
                 pynvml.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
             }
-            while not self._stop.is_set():
-                self.samples.append(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM))
-                r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                for bit, n in names.items():
-                    if r & bit:
-                        self.reasons.add(n)
-                self._stop.wait(self.period)
+            self._sample()   # the calls are warm before the region starts; this sample is dropped
+            self.samples.clear()
+            self.reasons.clear()
         except Exception as e:   # NVML missing: report that instead of clocks
+            self._nvml = None
             self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
 
+    @staticmethod
+    def _handle_for(pynvml, cuda_index):
+        """NVML handle of a CUDA device: by UUID (CUDA_VISIBLE_DEVICES may renumber devices), else by index."""
+        try:
+            uuid = str(torch.cuda.get_device_properties(cuda_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            return pynvml.nvmlDeviceGetHandleByUUID(uuid)
+        except Exception:
+            return pynvml.nvmlDeviceGetHandleByIndex(cuda_index)
+
+    def _sample(self):
+        self.samples.append(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM))
+        r = self._nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        for bit, n in self._names.items():
+            if r & bit:
+                self.reasons.add(n)
+
+    def _run(self):
+        try:
+            while not self._stop.is_set():
+                self._sample()
+                self._stop.wait(self.period)
+        except Exception as e:
+            self.reasons.add(f"nvml_error:{type(e).__name__}")
+
     def __enter__(self):
-        self._thread.start()
+        if self._nvml is not None:
+            self._stop.clear()
+            self._thread = self._threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
         return self
 
     def __exit__(self, *exc):
         self._stop.set()
-        self._thread.join(2.0)
+        if self._thread is not None:
+            self._thread.join(2.0)
+            self._thread = None
 
     def summary(self) -> dict:
         s = sorted(self.samples)
