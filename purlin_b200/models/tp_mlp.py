@@ -34,6 +34,8 @@ class TensorParallelMLP:
         self.w_down = init(hidden, self.i_local)      # this rank's rows of the down projection, [H, I / W]
         self.w_gu = interleave_gate_up(self.w_gate, self.w_up)
         self.h = torch.empty(tokens, self.i_local, dtype=torch.bfloat16, device=dev)
+        self._feed = None
+        self._y = None
 
     def forward(self, x_local: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         t = x_local.shape[0] * self.tp.world
@@ -42,6 +44,27 @@ class TensorParallelMLP:
         return self.tp.gemm_rs(h, self.w_down, out)
 
     __call__ = forward
+
+    def run_host_batches(self, host_batches, out: Optional[torch.Tensor] = None, on_result=None):
+        """Serving loop over activations that live in pinned host memory: one forward per batch, its input copied to the
+        device and its metric (the L2 norm of this rank's output rows) read back to the host every step, with both
+        transfers overlapped with the neighbouring steps (``purlin_b200.utils.feed.HostFeed``). Returns the metrics."""
+        from ..utils.feed import HostFeed
+        rows = self.tokens // self.tp.world
+        if self._feed is None:
+            self._feed = HostFeed((rows, self.hidden), torch.bfloat16, self.tp.device)
+        y = out if out is not None else self._y_rows(rows)
+
+        def step(x_dev):
+            self.forward(x_dev, y)
+            return torch.linalg.vector_norm(y, dtype=torch.float32)
+
+        return self._feed.run(host_batches, step, on_result)
+
+    def _y_rows(self, rows: int) -> torch.Tensor:
+        if self._y is None or self._y.shape[0] != rows:
+            self._y = torch.empty(rows, self.hidden, dtype=torch.bfloat16, device=self.tp.device)
+        return self._y
 
     def flops(self, tokens: int) -> float:
         """Floating-point operations of one forward over ``tokens`` tokens, whole job (all ranks)."""
