@@ -277,6 +277,18 @@ def build_plan(collective, world, rank, nbytes=0, sizes=None, out_sizes=None, dt
     return plan, chosen
 
 
+def reduce_scatter_symm(symm_tensor, out, op: ReduceOp = ReduceOp.ADD, reduction_mode=ReductionMode.NON_DETERMINISTIC, blocks: int = 0):
+    """Reduce-scatter straight out of ``symm_empty`` input tensors (no staging pass): ``out`` receives the reduction over
+    ranks of this rank's slice. The inputs may be reused as soon as the call completes in stream order."""
+    return symm_tensor.reduce_scatter(out, int(op), _mode(reduction_mode), blocks)
+
+
+def all_gather_symm(symm_tensor, via_switch=None, blocks: int = 0):
+    """In-place all-gather of a ``symm_empty`` tensor of ``world`` slices: every rank's own slice is pushed into the same
+    slice of every peer's tensor (one switch-replicated store, or one store per peer)."""
+    return symm_tensor.all_gather_(via_switch, blocks)
+
+
 def check_plan(plan, world, src_bytes, dst_bytes, staging_size=STAGING_BUFFER_SIZE) -> str:
     """Static bounds check of a plan against one rank's buffer extents. Returns "" when sound, else the first violation
     (every plan ``build_plan`` or a collective call produces has already passed this check)."""

@@ -224,6 +224,10 @@ class SymmetricTensor:
         self.lib.purlin_symm_flag_bytes.argtypes = [C.c_int]
         self.lib.purlin_symm_all_reduce.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64),
                                                     C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_void_p]
+        self.lib.purlin_symm_reduce_scatter.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64),
+                                                        C.c_void_p, C.c_size_t, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_uint64, C.c_void_p]
+        self.lib.purlin_symm_all_gather.argtypes = [C.c_int, C.c_int, C.POINTER(C.c_uint64), C.c_uint64, C.POINTER(C.c_uint64),
+                                                    C.c_size_t, C.c_int, C.c_int, C.c_uint64, C.c_void_p]
         self.group = group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.device = torch.device(device)
@@ -247,6 +251,32 @@ class SymmetricTensor:
         rc = self.lib.purlin_symm_all_reduce(self.rank, self.world, self.data_ptrs, self.multicast_ptr, self.flag_ptrs, self.nbytes,
                                              int(buffer_type(self.dtype)), int(op), int(mode), blocks, mm_depth,
                                              timeout_ms * 1_000_000, torch.cuda.current_stream().cuda_stream)
+        _native.check(self.lib, rc)
+        return self.tensor
+
+    def _slice_bytes(self) -> int:
+        if self.nbytes % (32 * self.world):
+            raise ValueError("the tensor must split into one 32-byte aligned slice per rank")
+        return self.nbytes // self.world
+
+    def reduce_scatter(self, out: torch.Tensor, op: int = 0, mode: int = 0, blocks: int = 0, mm_depth: int = 8, timeout_ms: int = 10000):
+        """``out`` (an ordinary tensor of numel / world elements) receives the reduction over ranks of slice ``rank``."""
+        from .. import _native, buffer_type
+        n = self._slice_bytes()
+        if out.numel() * out.element_size() != n or not out.is_contiguous() or out.dtype != self.dtype:
+            raise ValueError("the output must be a contiguous tensor of numel / world elements of the same dtype")
+        rc = self.lib.purlin_symm_reduce_scatter(self.rank, self.world, self.data_ptrs, self.multicast_ptr, self.flag_ptrs, out.data_ptr(), n,
+                                                 int(buffer_type(self.dtype)), int(op), int(mode), blocks, mm_depth,
+                                                 timeout_ms * 1_000_000, torch.cuda.current_stream().cuda_stream)
+        _native.check(self.lib, rc)
+        return out
+
+    def all_gather_(self, via_switch=None, blocks: int = 0, timeout_ms: int = 10000):
+        """In place: slice ``rank`` of this rank's tensor is copied into slice ``rank`` of every rank's tensor."""
+        from .. import _native
+        sw = -1 if via_switch is None else int(bool(via_switch))
+        rc = self.lib.purlin_symm_all_gather(self.rank, self.world, self.data_ptrs, self.multicast_ptr, self.flag_ptrs, self._slice_bytes(),
+                                             sw, blocks, timeout_ms * 1_000_000, torch.cuda.current_stream().cuda_stream)
         _native.check(self.lib, rc)
         return self.tensor
 

@@ -210,6 +210,30 @@ def main():
                 if rank == 0:
                     print(bench.csv_row(coll, "purlin_b200:symm-zero-copy", world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
                 del stt
+            if coll == "rs" and args.symm and not args.tune:
+                # inputs in symmetric memory: peers (or the switch) read them in place, no staging pass
+                stt = purlin.symm_empty((in_b // esz,), td, h)
+                stt.tensor.copy_(x)
+                out.fill_(7)
+                purlin.reduce_scatter_symm(stt, out)
+                oks = stt.status() == 0 and torch.equal(out, expect)
+                t = bench.measure(lambda: purlin.reduce_scatter_symm(stt, out), args.warmup, runs, args.graph)
+                if rank == 0:
+                    print(bench.csv_row(coll, "purlin_b200:symm-zero-copy", world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
+                del stt
+            if coll == "ag" and args.symm and not args.tune:
+                # the gathered tensor lives in symmetric memory: every rank pushes its slice into all of them in place
+                stt = purlin.symm_empty((out.numel(),), td, h)
+                per = x.numel()
+                for via, tag in ((None, "symm-zero-copy"), (False, "symm-zero-copy:stores"), (True, "symm-zero-copy:switch")):
+                    stt.tensor.fill_(7)
+                    stt.tensor[rank * per:(rank + 1) * per].copy_(x.reshape(-1))
+                    purlin.all_gather_symm(stt, via_switch=via)
+                    oks = stt.status() == 0 and torch.equal(stt.tensor, expect.reshape(-1))
+                    t = bench.measure(lambda: purlin.all_gather_symm(stt, via_switch=via), args.warmup, runs, args.graph)
+                    if rank == 0:
+                        print(bench.csv_row(coll, "purlin_b200:" + tag, world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
+                del stt
             if not args.no_nccl:
                 t = bench.measure(nccl_timed, args.warmup, runs, args.graph)
                 if rank == 0:

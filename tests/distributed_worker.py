@@ -210,6 +210,31 @@ def main():
                     failures.append(f"symm all-reduce {dtype} mode {int(mode)} rep {rep}")
         count += 1
         del st
+    # zero-copy reduce-scatter (symmetric inputs -> ordinary output) and in-place all-gather of a symmetric tensor
+    for dtype, code, n_slice in ((torch.bfloat16, 0, 1 << 18), (torch.float32, 4, 8 * 11)):
+        st = purlin.symm_empty((W * n_slice,), dtype, h)
+        out_rs = torch.empty(n_slice, dtype=dtype, device=dev)
+        for mode in (purlin.ReductionMode.NON_DETERMINISTIC, purlin.ReductionMode.DETERMINISTIC):
+            for rep in range(2):
+                parts = [ints(W * n_slice, code, 1300 + rep * 10 + r) for r in range(W)]
+                st.tensor.copy_(parts[rank].to(dev))
+                out_rs.fill_(7.0)
+                purlin.reduce_scatter_symm(st, out_rs, reduction_mode=mode)
+                st.tensor.fill_(9.0)     # the inputs may be overwritten as soon as the call is done in stream order
+                exp = expected(RS, W, rank, parts, n_slice * parts[0].element_size(), None, code)
+                if st.status() != 0 or not torch.equal(out_rs.cpu().view(torch.uint8), exp.view(torch.uint8)):
+                    failures.append(f"symm reduce-scatter {dtype} mode {int(mode)} rep {rep} status {st.status()}")
+        for via in (None, False, True):
+            for rep in range(2):
+                parts = [ints(n_slice, code, 1500 + rep * 10 + r) for r in range(W)]
+                st.tensor.fill_(5.0)
+                st.tensor[rank * n_slice:(rank + 1) * n_slice].copy_(parts[rank].to(dev))
+                purlin.all_gather_symm(st, via_switch=via)
+                exp = torch.cat(parts)
+                if st.status() != 0 or not torch.equal(st.tensor.cpu().view(torch.uint8), exp.view(torch.uint8)):
+                    failures.append(f"symm all-gather {dtype} via_switch {via} rep {rep} status {st.status()}")
+        count += 1
+        del st
     purlin.finalize(h)
     purlin.finalize(h)
     ok = torch.tensor([0 if failures else 1], device=dev)
