@@ -76,6 +76,20 @@ def _worker(rank, world, port, what, q):
             purlin.all_to_all_v(xa, outa, splits_in + splits_out, h, 0)
             refa = torch.cat([torch.full((splits_out[q],), q, dtype=torch.uint8) for q in range(world)])
             ok = ok and torch.equal(outa, refa)
+        elif what == "sequence_parallel":
+            from purlin_b200.parallel import sequence_parallel as sp
+            s_local, heads, d = 8, 2 * world, 4
+            g = torch.Generator().manual_seed(7)
+            whole = torch.randn(s_local * world, heads, d, generator=g)      # the same on every rank
+            mine = whole[rank * s_local:(rank + 1) * s_local].clone()
+            hg = heads // world
+            by_heads = sp.seq_to_heads(mine, h)
+            ok = torch.equal(by_heads, whole[:, rank * hg:(rank + 1) * hg])
+            ok = ok and torch.equal(sp.heads_to_seq(by_heads, h), mine)
+            ok = ok and torch.equal(sp.gather_sequence(mine, h), whole)
+            for step in (1, world - 1, world):
+                src = (rank - step) % world
+                ok = ok and torch.equal(sp.ring_shift(mine, h, step=step), whole[src * s_local:(src + 1) * s_local])
         purlin.finalize(h, 0)
         purlin.finalize(h, 0)   # idempotent
         q.put((rank, bool(ok), ""))
@@ -86,9 +100,10 @@ def _worker(rank, world, port, what, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("what", ["all_reduce", "all_gather", "others"])
-def test_gloo_world2(what):
-    world, port = 2, _free_port()
+@pytest.mark.parametrize("what,world", [("all_reduce", 2), ("all_gather", 2), ("others", 2), ("sequence_parallel", 2),
+                                        ("sequence_parallel", 3), ("others", 3)])
+def test_gloo_world2(what, world):
+    port = _free_port()
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=_worker, args=(r, world, port, what, q)) for r in range(world)]
