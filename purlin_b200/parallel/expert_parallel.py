@@ -13,7 +13,7 @@ from typing import Optional
 import torch
 
 from .. import _native
-from .symmetric import allocate_symmetric
+from .symmetric import allocate_symmetric, RawBuffer as _RawBuffer
 
 _declared = False
 
@@ -39,13 +39,6 @@ def _lib():
         lib.purlin_moe_combine.argtypes = [vp, vp, i, vp, vp, vp, i, vp]
         _declared = True
     return lib
-
-
-class _RawBuffer:
-    """A device pointer dressed as ``__cuda_array_interface__`` so torch can view symmetric memory without a copy."""
-
-    def __init__(self, ptr: int, shape, typestr: str):
-        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
 
 
 class ExpertParallelContext:

@@ -21,6 +21,13 @@ from typing import List, Tuple
 import torch
 
 
+class RawBuffer:
+    """A device pointer dressed as ``__cuda_array_interface__`` so torch can view symmetric memory without a copy."""
+
+    def __init__(self, ptr: int, shape, typestr: str):
+        self.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (ptr, False), "version": 3}
+
+
 def allocate_symmetric(nbytes: int, device: torch.device, group=None, provider: str | None = None):
     provider = provider or os.environ.get("PURLIN_PROVIDER", "torch")
     if provider == "torch":
@@ -242,8 +249,7 @@ class SymmetricTensor:
         self.data_ptrs = (C.c_uint64 * self.world)(*ptrs)
         self.flag_ptrs = (C.c_uint64 * self.world)(*[p + data_bytes for p in ptrs])
         self.multicast_ptr = int(mc or 0)
-        from .expert_parallel import _RawBuffer
-        raw = torch.as_tensor(_RawBuffer(ptrs[self.rank], (self.nbytes,), "|u1"), device=self.device)
+        raw = torch.as_tensor(RawBuffer(ptrs[self.rank], (self.nbytes,), "|u1"), device=self.device)
         self.tensor = raw.view(dtype).view(shape)
 
     def all_reduce_(self, op: int = 0, mode: int = 0, blocks: int = 0, mm_depth: int = 8, timeout_ms: int = 10000):
@@ -283,6 +289,5 @@ class SymmetricTensor:
     def status(self) -> int:
         """Synchronises and returns the status word of the flag block (0 = healthy)."""
         torch.cuda.synchronize(self.device)
-        from .expert_parallel import _RawBuffer
-        words = torch.as_tensor(_RawBuffer(int(self.flag_ptrs[self.rank]), (2 * self.world + 4,), "<i8"), device=self.device)
+        words = torch.as_tensor(RawBuffer(int(self.flag_ptrs[self.rank]), (2 * self.world + 4,), "<i8"), device=self.device)
         return int(words[2 * self.world + 2].item() & 0xffffffff)
