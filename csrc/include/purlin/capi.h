@@ -54,6 +54,9 @@ int purlin_context_clear_status(PurlinHostContext* ctx, void* stream);
 int purlin_context_set_timeout(PurlinHostContext* ctx, uint64_t timeoutNs);
 uint64_t purlin_context_seq(PurlinHostContext* ctx, void* stream);                 /* synchronises the stream */
 int purlin_context_has_multicast(PurlinHostContext* ctx);
+/* Device-side timing of recent calls (contexts created with PURLIN_TRACE=1): up to maxRecords records of four words
+ * {call sequence, start ns, end ns, payload bytes | collective << 56}, oldest first. Returns the count, -1 when off. */
+int purlin_context_trace(PurlinHostContext* ctx, uint64_t* out, int maxRecords, void* stream);
 const void* purlin_context_device_struct(PurlinHostContext* ctx);                   /* host copy of the device Context */
 size_t purlin_context_sizeof(void);
 

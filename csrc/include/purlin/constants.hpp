@@ -33,6 +33,7 @@ constexpr int kCounterSlots = kMaxSteps * kMaxChunks;
 
 // Flag value of chunk `k` (0-based) of call number `seq`. Values grow with
 // every call and every chunk, so flags are never cleared; waits compare >=.
+constexpr int kTraceSlots = 256;   // calls kept by the optional device-side timing ring
 constexpr int kSeqShift = 20;
 PURLIN_HD constexpr uint64_t flagValue(uint64_t seq, uint64_t chunk) {
   return (seq << kSeqShift) + chunk + 1;

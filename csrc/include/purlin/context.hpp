@@ -54,6 +54,7 @@ struct Context {
   uint32_t* counters;                    // [kCounterSlots] last-arrival counters, self-resetting
   uint32_t* exitCounter;                 // CTAs that finished the running call
   uint32_t* status;                      // [4]: code, step, peer, chunk
+  uint64_t* trace;                       // optional ring of kTraceSlots x {start ns, end ns, payload bytes, collective}; null = off
   size_t stagingTRSize;
   size_t packetStride;
   uint64_t timeoutNs;                    // time limit of every device wait

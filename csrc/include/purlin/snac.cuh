@@ -347,6 +347,13 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
   f.bulkDepth = plan.regime == int32_t(Regime::throughput) ? plan.stageDepth : 0;
   f.smem = dynSmem;
   bool ok = !sig::failed(ctx);    // a context that failed stays quiet until the host clears it
+  if (ctx.trace != nullptr && bIdx == 0 && threadIdx.x == 0) {
+    // device-side timing: the first CTA stamps the start of call `seq`, the last CTA out stamps its end
+    uint64_t* rec = ctx.trace + (f.seq % uint64_t(kTraceSlots)) * 4;
+    rec[0] = sig::globalTimerNs();
+    rec[2] = plan.payloadBytes;
+    rec[3] = uint64_t(uint32_t(plan.collective)) | (uint64_t(uint32_t(blocks)) << 32);
+  }
   if (ok && plan.varLenArrival && bIdx == 0) postArrival(ctx, f, plan.payloadBytes);
   for (int si = 0; si < plan.nSteps && ok; ++si) {
     const Step& s = plan.steps[si];
@@ -374,6 +381,7 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
     __threadfence();
     if (atomicAdd(ctx.exitCounter, 1u) == uint32_t(blocks - 1)) {
       *ctx.exitCounter = 0;
+      if (ctx.trace != nullptr) ctx.trace[(f.seq % uint64_t(kTraceSlots)) * 4 + 1] = sig::globalTimerNs();
       *ctx.seq = f.seq + 1;
       __threadfence();
     }

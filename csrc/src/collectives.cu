@@ -37,6 +37,7 @@ struct PurlinHostContext {
   WorkspaceLayout ws{};
   int device = 0;
   void* localBlock = nullptr;   // seq, exit counter, status, counters
+  void* traceRing = nullptr;    // device-side timing ring (PURLIN_TRACE=1), else null
   bool hasMulticast = false;
   // plans of fixed-size calls under the table/default policy, keyed by (collective, bytes, dtype, op, mode, in-place)
   std::unordered_map<uint64_t, Plan> planCache;
@@ -231,7 +232,13 @@ PurlinHostContext* purlin_context_create(int rank, int world, const uint64_t* pe
   c.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
   c.status = reinterpret_cast<uint32_t*>(lb + 128);
   c.counters = reinterpret_cast<uint32_t*>(lb + 256);
-  if (cudaStreamSynchronize(s) != cudaSuccess) { cudaFree(h->localBlock); delete h; setError("context set-up failed on the stream"); return nullptr; }
+  if (const char* t = std::getenv("PURLIN_TRACE"); t && t[0] != '0') {
+    // opt-in: every call leaves {start, end, bytes, collective} in a ring of kTraceSlots records (purlin_context_trace)
+    if (cudaMalloc(&h->traceRing, size_t(kTraceSlots) * 32) != cudaSuccess) { cudaFree(h->localBlock); delete h; setError("cudaMalloc of the trace ring failed"); return nullptr; }
+    cudaMemsetAsync(h->traceRing, 0, size_t(kTraceSlots) * 32, s);
+    c.trace = static_cast<uint64_t*>(h->traceRing);
+  }
+  if (cudaStreamSynchronize(s) != cudaSuccess) { cudaFree(h->localBlock); if (h->traceRing) cudaFree(h->traceRing); delete h; setError("context set-up failed on the stream"); return nullptr; }
   return h;
 }
 
@@ -239,6 +246,7 @@ int purlin_context_destroy(PurlinHostContext* h, void* stream) {
   if (!h) return 0;
   cudaStreamSynchronize(static_cast<cudaStream_t>(stream));   // in-flight collectives still use the counters
   if (h->localBlock) cudaFree(h->localBlock);
+  if (h->traceRing) cudaFree(h->traceRing);
   delete h;
   return 0;
 }
@@ -262,6 +270,32 @@ uint64_t purlin_context_seq(PurlinHostContext* h, void* stream) {
   return v;
 }
 int purlin_context_has_multicast(PurlinHostContext* h) { return h->hasMulticast ? 1 : 0; }
+
+// Device-side timing of the most recent calls (contexts created with PURLIN_TRACE=1). Synchronises the stream and
+// writes up to maxRecords records of four words {call sequence, start ns, end ns, payload bytes | collective << 56},
+// oldest first; returns how many, or -1 when tracing is off.
+int purlin_context_trace(PurlinHostContext* h, uint64_t* out, int maxRecords, void* stream) {
+  if (!h || !h->traceRing) return -1;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  std::vector<uint64_t> ring(size_t(kTraceSlots) * 4);
+  uint64_t seq = 0;
+  if (cudaMemcpyAsync(ring.data(), h->traceRing, ring.size() * 8, cudaMemcpyDeviceToHost, s) != cudaSuccess ||
+      cudaMemcpyAsync(&seq, h->dev.seq, 8, cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) {
+    setError("reading the trace ring failed");
+    return -1;
+  }
+  const uint64_t have = seq < uint64_t(kTraceSlots) ? seq : uint64_t(kTraceSlots);
+  const uint64_t want = have < uint64_t(maxRecords > 0 ? maxRecords : 0) ? have : uint64_t(maxRecords > 0 ? maxRecords : 0);
+  for (uint64_t i = 0; i < want; ++i) {
+    const uint64_t call = seq - want + i;
+    const uint64_t* rec = ring.data() + (call % uint64_t(kTraceSlots)) * 4;
+    out[i * 4 + 0] = call;
+    out[i * 4 + 1] = rec[0];
+    out[i * 4 + 2] = rec[1];
+    out[i * 4 + 3] = (rec[2] & ((uint64_t(1) << 56) - 1)) | ((rec[3] & 0xffu) << 56);
+  }
+  return int(want);
+}
 const void* purlin_context_device_struct(PurlinHostContext* h) { return &h->dev; }
 
 int purlin_collective(PurlinHostContext* h, int collective, const void* src, void* dst, size_t bytes,

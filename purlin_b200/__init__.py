@@ -180,6 +180,36 @@ def check(handle: ContextHandle, stream_ptr: Optional[int] = None) -> None:
         raise TimeoutError(f"purlin: device wait timed out ({names.get(out[0], out[0])}; step {out[1]}, peer {out[2]}, chunk {out[3]})")
 
 
+_COLLECTIVE_NAMES = ["all_reduce", "all_gather", "all_gather_v", "reduce_scatter", "reduce_scatter_v", "all_to_all", "all_to_all_v"]
+
+
+def read_trace(lib, ctx, stream: int, max_records: int = 256):
+    """Decodes the device-side timing ring of a native context (see ``trace``)."""
+    lib.purlin_context_trace.argtypes = [C.c_void_p, C.POINTER(C.c_uint64), C.c_int, C.c_void_p]
+    buf = (C.c_uint64 * (4 * max_records))()
+    n = lib.purlin_context_trace(ctx, buf, max_records, stream)
+    if n < 0:
+        return None
+    out = []
+    for i in range(n):
+        call, start, end, packed = (int(buf[4 * i + k]) for k in range(4))
+        kind = packed >> 56
+        out.append({"call": call, "collective": _COLLECTIVE_NAMES[kind] if kind < len(_COLLECTIVE_NAMES) else str(kind),
+                    "bytes": packed & ((1 << 56) - 1), "start_ns": start, "end_ns": end, "us": (end - start) / 1000.0})
+    return out
+
+
+def trace(handle: ContextHandle, stream_ptr: Optional[int] = None, max_records: int = 256):
+    """Device-side timing of the most recent collectives on this context, oldest first: one dict per call with the call
+    number, collective, payload bytes of the plan (all-reduce: the buffer; all-gather: bytes per rank; reduce-scatter and
+    all-to-all: this rank's whole input) and the device timestamps taken by the first CTA in and the last CTA out.
+    Needs ``PURLIN_TRACE=1`` in the environment when the context is created; returns ``None`` otherwise.
+    Synchronises the stream."""
+    if handle.cpu is not None or handle.ctx is None:
+        return None
+    return read_trace(handle.mod, handle.ctx, _stream(stream_ptr), max_records)
+
+
 def clear_status(handle: ContextHandle, stream_ptr: Optional[int] = None) -> None:
     if handle.cpu is None and handle.ctx is not None:
         _native.check(handle.mod, handle.mod.purlin_context_clear_status(handle.ctx, _stream(stream_ptr)))

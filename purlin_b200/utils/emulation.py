@@ -63,6 +63,11 @@ class EmulatedWorld:
     def seq(self, rank: int) -> int:
         return int(self.lib.purlin_context_seq(self.ctxs[rank], self.stream))
 
+    def trace(self, rank: int):
+        """Device-side timing records of one virtual rank (``PURLIN_TRACE=1`` at construction), or None."""
+        from .. import read_trace
+        return read_trace(self.lib, self.ctxs[rank], self.stream)
+
     def close(self):
         for h in self.ctxs:
             self.lib.purlin_context_destroy(h, self.stream)

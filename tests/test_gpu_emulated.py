@@ -164,3 +164,27 @@ def test_bulk_async_engine_cyclic(worlds, world):
     st = 256 << 10
     for coll, n in ((AG, 1 << 20), (RS, 1 << 19), (A2A, 1 << 19), (AR, 1 << 20)):
         run_case(worlds(world, st), coll, nbytes=n, dtype=4, pol=policy(chunkBytes=32768, arPath=0, stageDepth=6))
+
+
+def test_device_side_trace(monkeypatch):
+    """PURLIN_TRACE=1: every call leaves its device timestamps, logical bytes and kind in the context's ring."""
+    from purlin_b200.utils.emulation import EmulatedWorld
+    quiet = EmulatedWorld(2, 1 << 20)
+    assert quiet.trace(0) is None                       # off unless asked for
+    quiet.close()
+    monkeypatch.setenv("PURLIN_TRACE", "1")
+    ew = EmulatedWorld(2, 1 << 20)
+    try:
+        sizes = [4096, 65536, 4096 * 3]
+        for n in sizes:
+            run_case(ew, AG, nbytes=n, dtype=0, reps=1)
+        run_case(ew, AR, nbytes=2 * 32 * 100, dtype=4, reps=1)
+        for r in range(2):
+            rec = ew.trace(r)
+            assert [x["call"] for x in rec] == [0, 1, 2, 3]
+            assert [x["collective"] for x in rec] == ["all_gather"] * 3 + ["all_reduce"]
+            assert [x["bytes"] for x in rec[:3]] == sizes            # all-gather: bytes per rank
+            assert all(x["end_ns"] >= x["start_ns"] > 0 and x["us"] < 1e6 for x in rec)
+            assert all(b["start_ns"] >= a["start_ns"] for a, b in zip(rec, rec[1:]))
+    finally:
+        ew.close()
