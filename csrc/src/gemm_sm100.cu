@@ -82,6 +82,7 @@ struct Params {
   __nv_bfloat16* partialBuf[kMaxRanks];// every rank's receive buffers: 2 parities x [world slots][M / world, N]
   uint64_t* tileReady[kMaxRanks];      // every rank's flags, [world][blocksPerRank][tilesN][4 row quarters]
   size_t partialParityStride;          // elements between the two parities
+  int epiPipe;                         // 1: the epilogue overlaps the next chunk's TMEM load with the current chunk's arithmetic
   int rsScratch;                       // 1: remote tiles leave through a shared-memory transpose (long contiguous runs per row)
 };
 
@@ -397,10 +398,8 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           }
         }
       }
-      for (int c0 = 0; c0 < p.bn && !viaScratch; c0 += 32) {
-        uint32_t r[32];
-        tc::tmemLoad32(taddr + uint32_t(c0), r);
-        tc::tmemLoadWait();
+      // One 32-column chunk of this warp's rows: convert (and activate) the accumulators and store them.
+      auto emitChunk = [&](const uint32_t (&r)[32], int c0) {
         const int col = n0 + c0;
         if constexpr (EPI == kEpiSwiglu) {
           // columns [c0, c0+16) are gate, [c0+16, c0+32) are up, both for output columns (n0 + c0) / 2 + [0, 16)
@@ -467,6 +466,31 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           if (row < p.M) {
             __nv_bfloat16* out = p.C + size_t(row) * p.ldc + col;
             storeChunkBf16(out, r, col, p.N, (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
+          }
+        }
+      };
+      if (!viaScratch) {
+        if (p.epiPipe && COMM != kCommRS) {
+          // software-pipelined: the next chunk's TMEM load is in flight while this chunk is converted and stored
+          uint32_t ra[32], rb[32];
+          tc::tmemLoad32(taddr, ra);
+          for (int c0 = 0; c0 < p.bn; c0 += 64) {
+            tc::tmemLoadWaitFor(ra);
+            const bool second = c0 + 32 < p.bn;
+            if (second) tc::tmemLoad32(taddr + uint32_t(c0 + 32), rb);
+            emitChunk(ra, c0);
+            if (second) {
+              tc::tmemLoadWaitFor(rb);
+              if (c0 + 64 < p.bn) tc::tmemLoad32(taddr + uint32_t(c0 + 64), ra);
+              emitChunk(rb, c0 + 32);
+            }
+          }
+        } else {
+          for (int c0 = 0; c0 < p.bn; c0 += 32) {
+            uint32_t r[32];
+            tc::tmemLoad32(taddr + uint32_t(c0), r);
+            tc::tmemLoadWait();
+            emitChunk(r, c0);
           }
         }
       }
@@ -604,6 +628,8 @@ bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas, i
   if (bn == 0) bn = chooseBn(M, N, epilogue);
   if (bn % 16 || bn < 16 || bn > kMaxBN || (epilogue == kEpiSwiglu && bn % 32)) { setError("tile width must be a multiple of 16 (32 for SwiGLU) up to 256"); return false; }
   p.M = M; p.N = N; p.K = K; p.bn = bn;
+  static const bool epiPipe = [] { const char* e = std::getenv("PURLIN_GEMM_EPI_PIPE"); return !e || e[0] != '0'; }();
+  p.epiPipe = epiPipe ? 1 : 0;
   if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
   p.tilesM = (M + kBM * ctas - 1) / (kBM * ctas); p.tilesN = (N + bn - 1) / bn;
   const int stageBytes = kABytes + (bn / ctas) * kBK * 2;
