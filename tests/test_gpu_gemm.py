@@ -11,7 +11,8 @@ def _rand(m, k, seed, scale=1.0):
 
 
 @pytest.mark.parametrize("m,n,k,bn", [(128, 256, 64, 0), (256, 512, 512, 256), (384, 448, 1024, 224), (1024, 1024, 4096, 0),
-                                       (200, 264, 72, 128), (128, 3584, 8192, 0), (4096, 7168, 1024, 0)])
+                                       (200, 264, 72, 128), (128, 3584, 8192, 0), (4096, 7168, 1024, 0),
+                                       (2560, 2048, 512, 0)])   # the last two leave a small final wave on 74 CTA pairs
 def test_gemm_matches_fp32_reference(m, n, k, bn):
     from purlin_b200.ops.gemm import gemm
     a, w = _rand(m, k, 1), _rand(n, k, 2, 0.05)
@@ -37,7 +38,18 @@ def test_gemm_exact_on_small_integers():
     assert torch.equal(out.float(), ref.to(torch.bfloat16).float())
 
 
-@pytest.mark.parametrize("m,i,k", [(256, 512, 256), (1024, 3584, 2048)])
+def test_partial_last_wave_is_exact_on_small_integers():
+    # 10 x 8 tiles on 74 CTA pairs: a full wave and a last wave of six tiles
+    from purlin_b200.ops.gemm import gemm
+    g = torch.Generator(device="cuda").manual_seed(1)
+    a = torch.randint(-2, 3, (2560, 256), generator=g, device="cuda").to(torch.bfloat16)
+    w = torch.randint(-1, 2, (2048, 256), generator=g, device="cuda").to(torch.bfloat16)
+    out = gemm(a, w)
+    ref = (a.float() @ w.float().t())
+    assert torch.equal(out.float(), ref.to(torch.bfloat16).float())
+
+
+@pytest.mark.parametrize("m,i,k", [(256, 512, 256), (1024, 3584, 2048), (2560, 1024, 512)])
 def test_swiglu_epilogue(m, i, k):
     from purlin_b200.ops.gemm import gemm_swiglu, interleave_gate_up
     a, wg, wu = _rand(m, k, 3), _rand(i, k, 4, 0.05), _rand(i, k, 5, 0.05)
