@@ -145,3 +145,22 @@ def test_vmm_provider_fails_cleanly_without_a_driver():
     assert not lib.purlin_vmm_create(0, 1 << 20, 0, 2)
     assert "vmm provider" in _native.last_error(lib)
     assert lib.purlin_vmm_multicast_supported(0) == -1
+
+
+def test_report_pairs_rows_with_the_baseline():
+    from purlin_b200.utils import report
+    lines = [
+        "NCCL version 2.28.9+cuda12.9",
+        "collective,impl,world,totalBytes,datatype,lat(us),algbw(GB/s),busbw(GB/s),error(%),GPUName,warmup,runs,graph_launches",
+        "# cand rows are comments",
+        "ar,purlin_b200,8,1048576,bf16,20.00,52.4,91.7,0.000,NVIDIA B200,-,20,0",
+        "ar,purlin_b200:symm-zero-copy,8,1048576,bf16,16.00,65.5,114.7,0.000,NVIDIA B200,-,20,0",
+        "ar,nccl,8,1048576,bf16,40.00,26.2,45.9,0.000,NVIDIA B200,-,20,0",
+        "ag,purlin_b200,8,8192,bf16,10.00,0.8,0.7,100.000,NVIDIA B200,-,20,0",
+    ]
+    table = report.parse(lines)
+    assert list(table) == [("ar", 1048576), ("ag", 8192)]
+    assert table[("ar", 1048576)]["nccl"] == (40.0, 45.9, 0.0)
+    text = "\n".join(report.render(table, markdown=True))
+    assert "| AllReduce | 1 MiB | 20.0 (91.7) | 16.0 (114.7) | 40.0 (45.9) | 2.00x | 2.50x |" in text
+    assert "ERROR 100%" in text and "| AllGather | 8 KiB |" in text
