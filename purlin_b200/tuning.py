@@ -5,8 +5,11 @@ The reference freezes its tuning into compile-time structs per architecture and 
 (``bench_collectives.py --tune``) on the machine: for every collective and message size it records the policy
 (regime, variant, chunk size, CTA counts, NVLS on/off) that measured fastest.  Tables live in
 ``purlin_b200/tuning_tables/<gpu>_w<world>.json``; ``initialize`` installs the one that matches the GPU name and
-world size, and falls back to the built-in defaults when none exists.  ``PURLIN_TUNING_TABLE`` names a file to
-use instead; ``PURLIN_NO_TUNING_TABLE=1`` disables loading.
+world size.  A world size that was never swept borrows the table of the nearest measured world size of the same GPU
+(the larger one on a tie): protocol choice and chunk sizes depend far more on the message size than on the number of
+ranks, the layout engine re-fits CTA counts to the world, and a borrowed policy that does not fit a call falls back to
+the built-in bands like any other.  With no table at all the built-in bands apply.  ``PURLIN_TUNING_TABLE`` names a
+file to use instead; ``PURLIN_NO_TUNING_TABLE=1`` disables loading.
 """
 from __future__ import annotations
 
@@ -57,12 +60,29 @@ def install(table: dict, lib=None) -> int:
     return n
 
 
+def nearest_table(gpu_name: str, world: int) -> Optional[Path]:
+    """The table of the same GPU measured at the world size closest to ``world`` (the larger one on a tie), if any."""
+    stem = table_path(gpu_name, 0).name[:-len("0.json")]       # "<gpu>_w"
+    best = None
+    for p in sorted(TABLE_DIR.glob(stem + "*.json")):
+        try:
+            w = int(p.name[len(stem):-len(".json")])
+        except ValueError:
+            continue
+        rank = (abs(w - world), -w)
+        if best is None or rank < best[0]:
+            best = (rank, p)
+    return best[1] if best else None
+
+
 def load_for(gpu_name: str, world: int, lib=None) -> Optional[Path]:
     """Installs the table for this GPU and world size once per process; returns the file used, if any."""
     if os.environ.get("PURLIN_NO_TUNING_TABLE"):
         return None
     override = os.environ.get("PURLIN_TUNING_TABLE")
     path = Path(override) if override else table_path(gpu_name, world)
+    if not override and not path.exists():
+        path = nearest_table(gpu_name, world) or path          # never swept at this world size: borrow the neighbour's
     key = (str(path), world)
     if key in _installed:
         return path
@@ -71,7 +91,9 @@ def load_for(gpu_name: str, world: int, lib=None) -> Optional[Path]:
     with open(path) as f:
         table = json.load(f)
     if int(table.get("world", world)) != world:
-        return None
+        if override:
+            return None                                        # an explicit file must match
+        table = dict(table, world=world, entries=[dict(e, world=world) for e in table.get("entries", [])])
     install(table, lib)
     _installed.add(key)
     return path

@@ -208,3 +208,22 @@ def test_absent_rank_is_reported_not_hung(coll):
     assert status[0] in (1, 2, 3)
     status, _, _ = sim(coll, 4, policy=policy(regime=0), drop=1, **kw)
     assert status[0] in (1, 2, 3)
+
+
+@pytest.mark.parametrize("world", [3, 5, 6, 7, 12, 16])
+def test_borrowed_tuning_tables_give_sound_plans(world):
+    """A world size without its own measured table borrows the nearest one; every plan built from it must still pass
+    the interpreter bit for bit (policies that do not fit fall back to the built-in bands)."""
+    from purlin_b200 import tuning
+    tuning.clear()
+    try:
+        used = tuning.load_for("NVIDIA B200", world)
+        assert used is not None and f"_w{world}." not in used.name
+        for coll in (AR, AG, RS, A2A):
+            for n in (32 * world, 32 * world * 40, 32 * world * 1031, (1 << 20) // (32 * world) * (32 * world)):
+                status, outs, exp = sim(coll, world, nbytes=n, dtype=0, staging=4 << 20)
+                assert status[0] == 0, f"coll {coll} world {world} bytes {n}: status {status}"
+                for r in range(world):
+                    assert torch.equal(outs[r].view(torch.uint8), exp[r].view(torch.uint8)), f"coll {coll} world {world} bytes {n} rank {r}"
+    finally:
+        tuning.clear()

@@ -164,3 +164,32 @@ def test_report_pairs_rows_with_the_baseline():
     text = "\n".join(report.render(table, markdown=True))
     assert "| AllReduce | 1 MiB | 20.0 (91.7) | 16.0 (114.7) | 40.0 (45.9) | 2.00x | 2.50x |" in text
     assert "ERROR 100%" in text and "| AllGather | 8 KiB |" in text
+
+
+def test_unswept_world_size_borrows_the_nearest_table(tmp_path, monkeypatch):
+    import json
+    from purlin_b200 import tuning
+    monkeypatch.setattr(tuning, "TABLE_DIR", tmp_path)
+    monkeypatch.delenv("PURLIN_TUNING_TABLE", raising=False)
+    monkeypatch.delenv("PURLIN_NO_TUNING_TABLE", raising=False)
+    tuning.clear()
+    try:
+        def table(world, chunk):
+            pol = _native.Policy()
+            pol.regime, pol.threads, pol.putBlocks, pol.localBlocks, pol.consumeBlocks, pol.gatherBlocks = 1, 256, 8, 1, 16, 8
+            pol.lrBlocks, pol.mmDepth, pol.unroll, pol.arPath, pol.weighted, pol.chunkBytes = 2, 4, 4, 1, 1, chunk
+            return {"gpu": "Test GPU", "world": world, "entries": [{"collective": 0, "world": world, "bytes": 1 << 20, "policy": pol.as_dict()}]}
+        for world, chunk in ((4, 65536), (8, 131072)):
+            with open(tuning.table_path("Test GPU", world), "w") as f:
+                json.dump(table(world, chunk), f)
+        assert tuning.nearest_table("Test GPU", 6).name.endswith("_w8.json")      # tie between 4 and 8: the larger
+        assert tuning.nearest_table("Test GPU", 3).name.endswith("_w4.json")
+        assert tuning.nearest_table("Other GPU", 3) is None
+        used = tuning.load_for("Test GPU", 6)
+        assert used is not None and used.name.endswith("_w8.json")
+        _, chosen = purlin.build_plan(purlin.Collective.ALL_REDUCE, 6, 0, 6 * 32 * 4096, staging_size=8 << 20)
+        assert chosen.chunkBytes == 131072                                        # the borrowed band is in force at world 6
+        _, other = purlin.build_plan(purlin.Collective.ALL_REDUCE, 5, 0, 5 * 32 * 4096, staging_size=8 << 20)
+        assert other.chunkBytes != 131072                                         # nothing was installed for world 5
+    finally:
+        tuning.clear()
