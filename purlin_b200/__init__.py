@@ -332,10 +332,13 @@ Policy = _native.Policy
 
 
 def symm_empty(shape, dtype, handle_or_group=None, device=None):
-    """Allocates a tensor in symmetric memory (collective over the group). See ``all_reduce_symm``."""
-    from .parallel.symmetric import SymmetricTensor
+    """Allocates a tensor in symmetric memory (collective over the group). See ``all_reduce_symm``.
+    With a CPU handle the result is a gloo-backed stand-in with the same methods."""
+    from .parallel.symmetric import HostSymmetricTensor, SymmetricTensor
     group = getattr(handle_or_group, "group", handle_or_group)
     dev = device or getattr(handle_or_group, "device", None) or torch.device("cuda", torch.cuda.current_device())
+    if torch.device(dev).type == "cpu":
+        return HostSymmetricTensor(shape, dtype, group)
     return SymmetricTensor(shape, dtype, dev, group)
 
 

@@ -215,6 +215,66 @@ def allocate_emulated(nbytes: int, world: int, device: torch.device) -> Tuple[li
     return blocks, [b.data_ptr() for b in blocks]
 
 
+class HostSymmetricTensor:
+    """CPU stand-in for ``SymmetricTensor``: the same methods over a gloo process group, so code written against the
+    zero-copy API (gradient buckets, sharded parameters) runs and is tested without a GPU. Nothing is zero-copy here."""
+
+    _OPS = None
+
+    def __init__(self, shape, dtype, group=None):
+        import math
+        import torch.distributed as dist
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.device = torch.device("cpu")
+        self.dtype = dtype
+        numel = int(math.prod(shape)) if not isinstance(shape, int) else int(shape)
+        self.nbytes = numel * torch.empty(0, dtype=dtype).element_size()
+        if self.nbytes % 32:
+            raise ValueError("symmetric tensors must be a multiple of 32 bytes")
+        self.tensor = torch.zeros(shape, dtype=dtype)
+        self.multicast_ptr = 0
+
+    def _op(self, op: int):
+        import torch.distributed as dist
+        return {0: dist.ReduceOp.SUM, 1: dist.ReduceOp.PRODUCT, 2: dist.ReduceOp.MAX}[int(op)]
+
+    def _reduced(self, op: int) -> torch.Tensor:
+        import torch.distributed as dist
+        acc = self.tensor.to(torch.float32) if self.dtype in (torch.bfloat16, torch.float16) else self.tensor.clone()
+        dist.all_reduce(acc, op=self._op(op), group=self.group)      # fp32 accumulation, as on the device
+        return acc.to(self.dtype)
+
+    def all_reduce_(self, op: int = 0, mode: int = 0, blocks: int = 0, mm_depth: int = 8, timeout_ms: int = 10000):
+        self.tensor.copy_(self._reduced(op))
+        return self.tensor
+
+    def _slice_elems(self) -> int:
+        if self.nbytes % (32 * self.world):
+            raise ValueError("the tensor must split into one 32-byte aligned slice per rank")
+        return self.tensor.numel() // self.world
+
+    def reduce_scatter(self, out: torch.Tensor, op: int = 0, mode: int = 0, blocks: int = 0, mm_depth: int = 8, timeout_ms: int = 10000):
+        n = self._slice_elems()
+        if out.numel() != n or out.dtype != self.dtype:
+            raise ValueError("the output must be a contiguous tensor of numel / world elements of the same dtype")
+        out.copy_(self._reduced(op).reshape(-1)[self.rank * n:(self.rank + 1) * n].view_as(out))
+        return out
+
+    def all_gather_(self, via_switch=None, blocks: int = 0, timeout_ms: int = 10000):
+        import torch.distributed as dist
+        n = self._slice_elems()
+        flat = self.tensor.view(-1)
+        mine = flat[self.rank * n:(self.rank + 1) * n].clone().view(torch.uint8)     # gloo moves bytes of any element type
+        parts = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(parts, mine, group=self.group)
+        flat.view(torch.uint8).copy_(torch.cat(parts))
+        return self.tensor
+
+    def status(self) -> int:
+        return 0
+
+
 class SymmetricTensor:
     """A tensor in symmetric memory together with its peer mappings and the flag block the zero-copy collectives use.
 

@@ -90,6 +90,42 @@ def _worker(rank, world, port, what, q):
             for step in (1, world - 1, world):
                 src = (rank - step) % world
                 ok = ok and torch.equal(sp.ring_shift(mine, h, step=step), whole[src * s_local:(src + 1) * s_local])
+        elif what == "strategies":
+            from purlin_b200.parallel import data_parallel as dp
+            torch.manual_seed(0)
+            model = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.Tanh(), torch.nn.Linear(40, 8))
+            buckets = dp.GradientBuckets(model.parameters(), h, bucket_bytes=2048)
+            ok = len(buckets.buckets) >= 2
+            for step in range(2):
+                buckets.zero()
+                g = torch.Generator().manual_seed(10 * step + rank)
+                model(torch.randn(16, 24, generator=g)).square().mean().backward()
+                want = []
+                for p in model.parameters():
+                    t = p.grad.detach().clone()
+                    dist.all_reduce(t)
+                    want.append(t / world)
+                buckets.reduce(average=True)
+                ok = ok and all(torch.allclose(p.grad, t, rtol=1e-5, atol=1e-7) for p, t in zip(model.parameters(), want))
+            sh = dp.ShardedFlatParameter(100 * world + 3, torch.float32, h)
+            sh.shard.fill_(float(rank + 1))
+            full = sh.gather()
+            ok = ok and full.numel() == 100 * world + 3
+            for peer in range(world):
+                ok = ok and bool(torch.all(sh.full.tensor[peer * sh.slice_elems:(peer + 1) * sh.slice_elems] == float(peer + 1)))
+            sh.grad_full.tensor.copy_(torch.arange(sh.slice_elems * world, dtype=torch.float32) % 5 + rank)
+            got = sh.reduce_scatter_grad(average=False)
+            base = torch.arange(sh.slice_elems * world, dtype=torch.float32)[rank * sh.slice_elems:(rank + 1) * sh.slice_elems] % 5
+            ok = ok and torch.equal(got, base * world + sum(range(world)))
+            # the same surface on 16-bit elements
+            st = purlin.symm_empty((64 * world,), torch.bfloat16, h)
+            st.tensor.fill_(float(rank + 1))
+            purlin.all_reduce_symm(st)
+            ok = ok and bool(torch.all(st.tensor == float(sum(range(1, world + 1)))))
+            st.tensor.zero_()
+            st.tensor[rank * 64:(rank + 1) * 64] = float(rank + 7)
+            purlin.all_gather_symm(st)
+            ok = ok and all(bool(torch.all(st.tensor[peer * 64:(peer + 1) * 64] == float(peer + 7))) for peer in range(world))
         purlin.finalize(h, 0)
         purlin.finalize(h, 0)   # idempotent
         q.put((rank, bool(ok), ""))
@@ -101,7 +137,7 @@ def _worker(rank, world, port, what, q):
 
 
 @pytest.mark.parametrize("what,world", [("all_reduce", 2), ("all_gather", 2), ("others", 2), ("sequence_parallel", 2),
-                                        ("sequence_parallel", 3), ("others", 3)])
+                                        ("sequence_parallel", 3), ("others", 3), ("strategies", 2), ("strategies", 3)])
 def test_gloo_world2(what, world):
     port = _free_port()
     ctx = mp.get_context("spawn")
