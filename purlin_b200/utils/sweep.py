@@ -77,6 +77,83 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
     return out
 
 
+def variable_length_section(args, h, rank, world, dev, td, esz):
+    """AllGatherV, ReduceScatterV and AllToAllV at per-rank element counts uniform in [0.5, 1.5] x ``args.variable`` (seed 7,
+    multiples of 16 elements), against NCCL on buffers padded to the largest count (the usual way to run uneven sizes on a
+    library that wants equal ones). Inputs are integers in [-2, 2] generated on the device (seed 42 + rank), so the untimed
+    comparison with NCCL's result is exact in any summation order."""
+    from .split_policy import uniform_counts
+    unit = max(32 // esz, 1)
+    counts = uniform_counts(world, base_elems=args.variable, seed=7, multiple=unit)
+    sizes = [c * esz for c in counts]
+    total, biggest = sum(sizes), max(counts)
+    gen = torch.Generator(device=dev).manual_seed(42 + rank)
+
+    def ints(n):
+        return torch.randint(-2, 3, (n,), generator=gen, device=dev).to(td)
+
+    def row(coll, impl, t, ok=True, logical=None):
+        if rank == 0:
+            print(bench.csv_row(coll, impl, world, total if logical is None else logical, args.dtype, t, 0.0 if ok else 100.0), flush=True)
+
+    def agree(ok):
+        flag = torch.tensor([1 if ok else 0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return bool(flag.item())
+
+    # all-gather-v: rank r contributes counts[r] elements
+    x, out = ints(counts[rank]), torch.empty(sum(counts), dtype=td, device=dev)
+    xp = torch.zeros(biggest, dtype=td, device=dev)
+    xp[:counts[rank]] = x
+    outp = torch.empty(world * biggest, dtype=td, device=dev)
+    dist.all_gather_into_tensor(outp, xp)
+    purlin.all_gather_v(x, out, sizes, h, None)
+    purlin.check(h)
+    ok, off = True, 0
+    for q in range(world):
+        ok = ok and torch.equal(out[off:off + counts[q]], outp[q * biggest:q * biggest + counts[q]])
+        off += counts[q]
+    row("agv", "purlin_b200", bench.measure(lambda: purlin.all_gather_v(x, out, sizes, h, None), args.warmup, args.runs, args.graph), agree(ok))
+    if not args.no_nccl:
+        row("agv", "nccl:padded", bench.measure(lambda: dist.all_gather_into_tensor(outp, xp), args.warmup, args.runs, args.graph))
+    del xp, outp
+
+    # reduce-scatter-v: every rank holds sum(counts) elements, rank r receives counts[r] of the sum
+    x, out = ints(sum(counts)), torch.empty(counts[rank], dtype=td, device=dev)
+    ref = x.clone()
+    dist.all_reduce(ref)
+    purlin.reduce_scatter_v(x, out, sizes, h, None)
+    purlin.check(h)
+    off = sum(counts[:rank])
+    ok = torch.equal(out, ref[off:off + counts[rank]])
+    del ref
+    row("rsv", "purlin_b200", bench.measure(lambda: purlin.reduce_scatter_v(x, out, sizes, h, None), args.warmup, args.runs, args.graph), agree(ok))
+    if not args.no_nccl:
+        xp = torch.zeros(world * biggest, dtype=td, device=dev)
+        outp = torch.empty(biggest, dtype=td, device=dev)
+        row("rsv", "nccl:padded", bench.measure(lambda: dist.reduce_scatter_tensor(outp, xp), args.warmup, args.runs, args.graph))
+        del xp, outp
+
+    # all-to-all-v: rank r sends counts[(r + q) % world] / world elements to rank q (rows are rotations of one list)
+    def cell(r, q):
+        return (counts[(r + q) % world] // world) // unit * unit
+
+    send = [cell(rank, q) for q in range(world)]
+    recv = [cell(q, rank) for q in range(world)]
+    x, out = ints(sum(send)), torch.empty(sum(recv), dtype=td, device=dev)
+    ref = torch.empty_like(out)
+    dist.all_to_all_single(ref, x, output_split_sizes=recv, input_split_sizes=send)
+    splits = [c * esz for c in send] + [c * esz for c in recv]
+    purlin.all_to_all_v(x, out, splits, h, None)
+    purlin.check(h)
+    ok = torch.equal(out, ref)
+    moved = sum(cell(0, q) for q in range(world)) * esz * world     # what rank 0 sends, times the ranks: the reference's convention
+    row("a2av", "purlin_b200", bench.measure(lambda: purlin.all_to_all_v(x, out, splits, h, None), args.warmup, args.runs, args.graph), agree(ok), moved)
+    if not args.no_nccl:
+        row("a2av", "nccl", bench.measure(lambda: dist.all_to_all_single(ref, x, output_split_sizes=recv, input_split_sizes=send),
+                                          args.warmup, args.runs, args.graph), True, moved)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--collectives", default="ar,ag,rs,a2a")
@@ -90,6 +167,8 @@ def main():
     ap.add_argument("--tune", action="store_true")
     ap.add_argument("--no-nccl", action="store_true")
     ap.add_argument("--symm", action="store_true", help="also time the zero-copy all-reduce on symmetric tensors")
+    ap.add_argument("--variable", type=int, default=0, metavar="ELEMS",
+                    help="also run the variable-length collectives: per-rank counts uniform in [0.5, 1.5] x ELEMS from seed 7")
     ap.add_argument("--csv", default="")
     ap.add_argument("--table-out", default="")
     args = ap.parse_args()
@@ -239,6 +318,8 @@ def main():
                 if rank == 0:
                     print(bench.csv_row(coll, "nccl", world, total, args.dtype, t), flush=True)
             n *= args.factor
+    if args.variable:
+        variable_length_section(args, h, rank, world, dev, td, esz)
     if args.tune and rank == 0:
         from purlin_b200 import tuning
         path = args.table_out or os.path.join("tuning_out", str(tuning.table_path(torch.cuda.get_device_name(), world).name))
