@@ -133,9 +133,36 @@ inline Policy defaultPolicy(const CollectiveSpec& s, const WorkspaceLayout& ws) 
   return p;
 }
 
+// The fixed-size collective whose measured bands a variable-length call may borrow.
+inline bool fixedSibling(CollectiveType t, CollectiveType& out) {
+  switch (t) {
+    case CollectiveType::allGatherV: out = CollectiveType::allGather; return true;
+    case CollectiveType::reduceScatterV: out = CollectiveType::reduceScatter; return true;
+    case CollectiveType::allToAllV: out = CollectiveType::allToAll; return true;
+    default: return false;
+  }
+}
+
 inline Policy selectPolicy(const CollectiveSpec& s, const WorkspaceLayout& ws) {
   Policy p;
-  if (TuningTable::global().lookup(s.type, s.world, dispatchBytes(s), p)) {
+  const TuningTable& table = TuningTable::global();
+  bool found = table.lookup(s.type, s.world, dispatchBytes(s), p);
+  if (!found) {
+    // No band measured for a variable-length form: borrow the band its fixed-size sibling measured for the largest
+    // stream of this call (CTA counts and chunk size carry over; the switch variants were measured for whole, equal
+    // slices only and are dropped). A borrowed policy that does not fit the call falls back like any other (planFor).
+    CollectiveType sibling;
+    if (fixedSibling(s.type, sibling) && table.lookup(sibling, s.world, dispatchBytes(s), p)) {
+      const Policy builtIn = defaultPolicy(s, ws);
+      if (s.type == CollectiveType::allToAllV && p.regime != int32_t(Regime::throughput)) return builtIn;   // packets are chosen per stream there
+      p.memType = int32_t(MemType::unicast);
+      p.lrMulticast = 0;
+      p.weighted = 1;
+      if (p.perStreamThreshold == 0) p.perStreamThreshold = builtIn.perStreamThreshold;
+      found = true;
+    }
+  }
+  if (found) {
     // a measured entry may ask for NVLS; drop it where this call cannot use it
     if (!s.multicastAvailable || s.mode == ReductionMode::deterministic) { p.memType = int32_t(MemType::unicast); p.lrMulticast = 0; }
     return p;

@@ -227,3 +227,30 @@ def test_borrowed_tuning_tables_give_sound_plans(world):
                     assert torch.equal(outs[r].view(torch.uint8), exp[r].view(torch.uint8)), f"coll {coll} world {world} bytes {n} rank {r}"
     finally:
         tuning.clear()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_variable_length_forms_borrow_measured_bands(world):
+    """With a measured table installed, AGV / RSV / A2AV take the CTA counts and chunk size of their fixed-size sibling's band
+    (never its switch variant) and still run bit for bit through the interpreter, whole range of stream sizes."""
+    from purlin_b200 import tuning
+    tuning.clear()
+    try:
+        assert tuning.load_for("NVIDIA B200", world) is not None
+        big = 3 << 20
+        sizes = [big // 32 * 32 if q % 2 == 0 else (big // 3) // 32 * 32 for q in range(world)]
+        _, fixed = P.build_plan(AG, world, 0, max(sizes), staging_size=64 << 20)
+        _, borrowed = P.build_plan(AGV, world, 0, 0, sizes=sizes, staging_size=64 << 20)
+        assert (borrowed.putBlocks, borrowed.consumeBlocks, borrowed.chunkBytes) == (fixed.putBlocks, fixed.consumeBlocks, fixed.chunkBytes)
+        _, rs = P.build_plan(RSV, world, 0, 0, sizes=sizes, staging_size=64 << 20, multicast=True)
+        assert rs.memType == 0                                    # the switch variant is not borrowed
+        for scale in (1, 40, 3000):
+            lst = [32 * scale * ((q * 5) % 4) for q in range(world)]
+            mat = [[32 * scale * ((r + 2 * q) % 3) for q in range(world)] for r in range(world)]
+            for coll, sz in ((AGV, lst), (RSV, lst), (A2AV, mat)):
+                status, outs, exp = sim(coll, world, sizes=sz, dtype=0, staging=4 << 20)
+                assert status[0] == 0, f"coll {coll} world {world} scale {scale}: {status}"
+                for r in range(world):
+                    assert torch.equal(outs[r].view(torch.uint8), exp[r].view(torch.uint8)), f"coll {coll} world {world} scale {scale} rank {r}"
+    finally:
+        tuning.clear()
