@@ -77,11 +77,13 @@ def candidates(coll: str, world: int, nbytes: int, layout: dict, multicast: bool
     return out
 
 
-def variable_length_section(args, h, rank, world, dev, td, esz):
+def variable_length_section(args, h, rank, world, dev, td, esz, table=None):
     """AllGatherV, ReduceScatterV and AllToAllV at per-rank element counts uniform in [0.5, 1.5] x ``args.variable`` (seed 7,
     multiples of 16 elements), against NCCL on buffers padded to the largest count (the usual way to run uneven sizes on a
     library that wants equal ones). Inputs are integers in [-2, 2] generated on the device (seed 42 + rank), so the untimed
-    comparison with NCCL's result is exact in any summation order."""
+    comparison with NCCL's result is exact in any summation order. With ``--tune`` the candidate policies of the fixed-size
+    sibling are measured for each form and the fastest exact one is appended to ``table`` under the form's own collective id,
+    keyed by the largest stream of the call (the size ``selectPolicy`` dispatches on)."""
     from .split_policy import uniform_counts
     unit = max(32 // esz, 1)
     counts = uniform_counts(world, base_elems=args.variable, seed=7, multiple=unit)
@@ -101,6 +103,36 @@ def variable_length_section(args, h, rank, world, dev, td, esz):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         return bool(flag.item())
 
+    def best_of(coll, sibling, kind, dispatch, call, correct, scrub):
+        """Default-policy row, and with --tune the fastest exact candidate (recorded in the table)."""
+        t = bench.measure(lambda: call(None), args.warmup, args.runs, args.graph)
+        if not (args.tune and table is not None):
+            return t
+        best = None
+        for label, pol in candidates(sibling, world, dispatch, h.layout, False):
+            if kind == purlin.Collective.ALL_TO_ALL_V and pol.regime != 1:
+                continue                                   # packets are chosen per stream inside an all-to-all-v plan
+            try:
+                scrub()                                    # a candidate that writes nothing must not pass on old results
+                call(pol)
+                purlin.check(h)
+                if not agree(correct()):
+                    continue
+                tc = bench.measure(lambda: call(pol), args.warmup, args.runs, args.graph)
+            except (RuntimeError, TimeoutError) as e:
+                if rank == 0:
+                    print(f"# skipped {coll} {label}: {e}", flush=True)
+                purlin.clear_status(h)
+                continue
+            if rank == 0:
+                print("# " + bench.csv_row(coll, f"cand:{label}:{pol.putBlocks}/{pol.consumeBlocks}/c{pol.chunkBytes >> 10}K", world, total, args.dtype, tc), flush=True)
+            if best is None or tc.us < best[0].us:
+                best = (tc, label, pol)
+        if best is not None and best[0].us < t.us:
+            table.append({"collective": int(kind), "world": world, "bytes": dispatch, "label": best[1], "us": best[0].us, "policy": best[2].as_dict()})
+            return best[0]
+        return t
+
     # all-gather-v: rank r contributes counts[r] elements
     x, out = ints(counts[rank]), torch.empty(sum(counts), dtype=td, device=dev)
     xp = torch.zeros(biggest, dtype=td, device=dev)
@@ -113,7 +145,15 @@ def variable_length_section(args, h, rank, world, dev, td, esz):
     for q in range(world):
         ok = ok and torch.equal(out[off:off + counts[q]], outp[q * biggest:q * biggest + counts[q]])
         off += counts[q]
-    row("agv", "purlin_b200", bench.measure(lambda: purlin.all_gather_v(x, out, sizes, h, None), args.warmup, args.runs, args.graph), agree(ok))
+    def agv_ok():
+        good, at = True, 0
+        for q in range(world):
+            good = good and torch.equal(out[at:at + counts[q]], outp[q * biggest:q * biggest + counts[q]])
+            at += counts[q]
+        return good
+
+    row("agv", "purlin_b200", best_of("agv", "ag", purlin.Collective.ALL_GATHER_V, max(sizes),
+                                      lambda pol: purlin.all_gather_v(x, out, sizes, h, None, policy=pol), agv_ok, lambda: out.fill_(7)), agree(ok))
     if not args.no_nccl:
         row("agv", "nccl:padded", bench.measure(lambda: dist.all_gather_into_tensor(outp, xp), args.warmup, args.runs, args.graph))
     del xp, outp
@@ -125,9 +165,12 @@ def variable_length_section(args, h, rank, world, dev, td, esz):
     purlin.reduce_scatter_v(x, out, sizes, h, None)
     purlin.check(h)
     off = sum(counts[:rank])
-    ok = torch.equal(out, ref[off:off + counts[rank]])
+    want = ref[off:off + counts[rank]].clone()
+    ok = torch.equal(out, want)
     del ref
-    row("rsv", "purlin_b200", bench.measure(lambda: purlin.reduce_scatter_v(x, out, sizes, h, None), args.warmup, args.runs, args.graph), agree(ok))
+    row("rsv", "purlin_b200", best_of("rsv", "rs", purlin.Collective.REDUCE_SCATTER_V, max(sizes),
+                                      lambda pol: purlin.reduce_scatter_v(x, out, sizes, h, None, policy=pol), lambda: torch.equal(out, want),
+                                      lambda: out.fill_(7)), agree(ok))
     if not args.no_nccl:
         xp = torch.zeros(world * biggest, dtype=td, device=dev)
         outp = torch.empty(biggest, dtype=td, device=dev)
@@ -148,7 +191,9 @@ def variable_length_section(args, h, rank, world, dev, td, esz):
     purlin.check(h)
     ok = torch.equal(out, ref)
     moved = sum(cell(0, q) for q in range(world)) * esz * world     # what rank 0 sends, times the ranks: the reference's convention
-    row("a2av", "purlin_b200", bench.measure(lambda: purlin.all_to_all_v(x, out, splits, h, None), args.warmup, args.runs, args.graph), agree(ok), moved)
+    row("a2av", "purlin_b200", best_of("a2av", "a2a", purlin.Collective.ALL_TO_ALL_V, max(max(send), max(recv)) * esz,
+                                       lambda pol: purlin.all_to_all_v(x, out, splits, h, None, policy=pol), lambda: torch.equal(out, ref),
+                                       lambda: out.fill_(7)), agree(ok), moved)
     if not args.no_nccl:
         row("a2av", "nccl", bench.measure(lambda: dist.all_to_all_single(ref, x, output_split_sizes=recv, input_split_sizes=send),
                                           args.warmup, args.runs, args.graph), True, moved)
@@ -319,7 +364,7 @@ def main():
                     print(bench.csv_row(coll, "nccl", world, total, args.dtype, t), flush=True)
             n *= args.factor
     if args.variable:
-        variable_length_section(args, h, rank, world, dev, td, esz)
+        variable_length_section(args, h, rank, world, dev, td, esz, table)
     if args.tune and rank == 0:
         from purlin_b200 import tuning
         path = args.table_out or os.path.join("tuning_out", str(tuning.table_path(torch.cuda.get_device_name(), world).name))
