@@ -193,3 +193,22 @@ def test_unswept_world_size_borrows_the_nearest_table(tmp_path, monkeypatch):
         assert other.chunkBytes != 131072                                         # nothing was installed for world 5
     finally:
         tuning.clear()
+
+
+def test_reference_arm_always_prints_one_json_line():
+    """`bench.py --impl reference` must exit 0 with one JSON line, whatever the state of the reference install."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for env_extra in ({}, {"WORLD_SIZE": "2", "RANK": "0"}):
+        env = dict(os.environ, **env_extra)
+        env.pop("PURLIN_REFERENCE_ARM", None)
+        res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--gpus", env_extra.get("WORLD_SIZE", "1")],
+                             capture_output=True, text=True, timeout=300, env=env)
+        assert res.returncode == 0, res.stderr[-2000:]
+        lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+        assert len(lines) == 1
+        rec = json.loads(lines[0])
+        assert rec["impl"] == "reference" and ("unavailable" in rec or "value" in rec)
