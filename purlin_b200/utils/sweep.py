@@ -214,6 +214,9 @@ def main():
     ap.add_argument("--symm", action="store_true", help="also time the zero-copy all-reduce on symmetric tensors")
     ap.add_argument("--variable", type=int, default=0, metavar="ELEMS",
                     help="also run the variable-length collectives: per-rank counts uniform in [0.5, 1.5] x ELEMS from seed 7")
+    ap.add_argument("--reference", default="", metavar="DIR",
+                    help="also time the reference's own collectives: DIR holds its installed package (purlin/) and, beside it, "
+                         "DIR_cache with its prebuilt binding module (see baseline/build_reference_module.py)")
     ap.add_argument("--csv", default="")
     ap.add_argument("--table-out", default="")
     args = ap.parse_args()
@@ -226,6 +229,13 @@ def main():
     if args.tune:
         os.environ["PURLIN_NO_TUNING_TABLE"] = "1"   # candidates are forced; the built-in policy is the fallback
     h = purlin.initialize(dist.group.WORLD, dev, 100, None)
+    ref_mod = ref_h = None
+    if args.reference:
+        # the reference's Python API, unmodified; its JIT finds the prebuilt module through its own cache directory
+        os.environ["PURLIN_CACHE_DIR"] = args.reference.rstrip("/") + "_cache"
+        sys.path.insert(0, args.reference)
+        import purlin as ref_mod   # noqa: E402  (the reference's package is called purlin; this one is purlin_b200)
+        ref_h = ref_mod.initialize(dist.group.WORLD, dev, 100, torch.cuda.current_stream().cuda_stream)
     td = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]
     esz = torch.empty(0, dtype=td).element_size()
     lo, hi = bench.parse_size(args.min_bytes), bench.parse_size(args.max_bytes)
@@ -358,6 +368,27 @@ def main():
                     if rank == 0:
                         print(bench.csv_row(coll, "purlin_b200:" + tag, world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
                 del stt
+            if ref_mod is not None and not args.tune:
+                rstream = torch.cuda.current_stream().cuda_stream
+                rout = torch.empty_like(out)
+
+                def ref_call():
+                    if coll == "ar":
+                        ref_mod.all_reduce(x, rout, ref_h, rstream)
+                    elif coll == "ag":
+                        ref_mod.all_gather(x, rout, ref_h, rstream)
+                    elif coll == "rs":
+                        ref_mod.reduce_scatter(x, rout, ref_h, rstream)
+                    else:
+                        ref_mod.all_to_all(x, rout, ref_h, rstream)
+
+                ref_call()
+                torch.cuda.synchronize()
+                okr = torch.equal(rout, expect)
+                t = bench.measure(ref_call, args.warmup, runs, args.graph)
+                if rank == 0:
+                    print(bench.csv_row(coll, "reference", world, total, args.dtype, t, 0.0 if okr else 100.0), flush=True)
+                del rout
             if not args.no_nccl:
                 t = bench.measure(nccl_timed, args.warmup, runs, args.graph)
                 if rank == 0:
@@ -372,6 +403,8 @@ def main():
         with open(path, "w") as f:
             json.dump({"gpu": torch.cuda.get_device_name(), "world": world, "dtype": args.dtype, "entries": table}, f, indent=1, sort_keys=True)
         print(f"# wrote {path}", flush=True)
+    if ref_mod is not None:
+        ref_mod.finalize(ref_h, torch.cuda.current_stream().cuda_stream)
     purlin.finalize(h)
     dist.destroy_process_group()
 
