@@ -212,3 +212,13 @@ def test_reference_arm_always_prints_one_json_line():
         assert len(lines) == 1
         rec = json.loads(lines[0])
         assert rec["impl"] == "reference" and ("unavailable" in rec or "value" in rec)
+
+
+def test_strategies_example_runs_on_cpu():
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "examples", "strategies.py"), "--cpu"], capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert "round trip exact: True" in res.stdout and "every entry 2.0" in res.stdout
