@@ -7,7 +7,6 @@
 // A single kernel template executes any Plan; it is instantiated per element
 // type and reduce operator for reductions and once for pure copies.
 #include <cuda_runtime.h>
-#include <nvtx3/nvToolsExt.h>
 
 #include <cstdio>
 #include <cstdlib>
@@ -21,6 +20,7 @@
 #include "purlin/capi.h"
 #include "purlin/layout.hpp"
 #include "purlin/snac.cuh"
+#include "purlin/telemetry.hpp"
 #include "purlin/tuning.hpp"
 
 namespace purlin {
@@ -139,20 +139,6 @@ const char* collectiveName(int c) {
   static const char* names[] = {"allReduce", "allGather", "allGatherV", "reduceScatter", "reduceScatterV", "allToAll", "allToAllV"};
   return c >= 0 && c < 7 ? names[c] : "collective";
 }
-
-struct NvtxRange {
-  explicit NvtxRange(const char* name, size_t bytes) {
-    nvtxEventAttributes_t a{};
-    a.version = NVTX_VERSION; a.size = NVTX_EVENT_ATTRIB_STRUCT_SIZE;
-    a.messageType = NVTX_MESSAGE_TYPE_ASCII; a.message.ascii = name;
-    a.payloadType = NVTX_PAYLOAD_TYPE_UNSIGNED_INT64; a.payload.ullValue = bytes;
-    static nvtxDomainHandle_t domain = nvtxDomainCreateA("Purlin");
-    domain_ = domain;
-    nvtxDomainRangePushEx(domain_, &a);
-  }
-  ~NvtxRange() { nvtxDomainRangePop(domain_); }
-  nvtxDomainHandle_t domain_;
-};
 
 int worldOneCopy(const CollectiveSpec& s, const void* src, void* dst, cudaStream_t stream) {
   // a world of one: every collective is a copy of the rank's own data

@@ -37,6 +37,7 @@
 #include "purlin/gemm.h"
 #include "purlin/layout.hpp"
 #include "purlin/tc_sm100.cuh"
+#include "purlin/telemetry.hpp"
 
 namespace purlin { void setError(const std::string& e); }
 using namespace purlin;
@@ -711,6 +712,7 @@ TpLayout tpLayout(int world, int M, int kAg, int nRs) {
 extern "C" {
 
 int purlin_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int bn, uint32_t* status, void* stream) {
+  NvtxRange range(epilogue == kEpiSwiglu ? "gemmSwiglu" : "gemm", size_t(M) * size_t(N) * 2);
   Params p{};
   const int ctas = ctasFor(M, M);
   if (!fillShape(p, M, N, K, epilogue, bn, ctas)) return 1;
@@ -767,6 +769,7 @@ int purlin_tp_clear_status(PurlinTpContext* c, void* stream) {
 }
 
 int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, void* out, int M, int N, int K, int epilogue, void* stream) {
+  NvtxRange range(epilogue == kEpiSwiglu ? "allGatherGemmSwiglu" : "allGatherGemm", size_t(M) * size_t(K) * 2);   // gathered bytes
   if (M > c->M || K > c->kAg || M % (c->world * kBM)) { setError("all-gather GEMM shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
   const int ctas = ctasFor(M, M / c->world);
@@ -802,6 +805,7 @@ int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, voi
 }
 
 int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* out, int M, int N, int K, void* stream) {
+  NvtxRange range("gemmReduceScatter", size_t(M) * size_t(N) * 2);   // bytes of the tensor that is reduce-scattered
   if (M > c->M || N > c->nRs || M % (c->world * kBM)) { setError("GEMM reduce-scatter shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
   const int ctas = ctasFor(M, M / c->world);

@@ -24,6 +24,7 @@
 #include "purlin/constants.hpp"
 #include "purlin/moe.h"
 #include "purlin/signal.cuh"
+#include "purlin/telemetry.hpp"
 
 namespace purlin { void setError(const std::string& e); }
 using namespace purlin;
@@ -367,6 +368,7 @@ void* purlin_moe_out_buffer(PurlinMoeContext* c) { return c->peers[c->rank] + c-
 
 int purlin_moe_route(PurlinMoeContext* c, const float* logits, int tokens, int normalize, int32_t* topkIdx, float* topkWeight,
                      int32_t* slot, void* stream) {
+  NvtxRange range("moeRoute", size_t(tokens));
   if (tokens > c->maxTokens) { setError("more tokens than the context was created for"); return 1; }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* counts = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(c->local) + 1024);
@@ -385,6 +387,7 @@ int purlin_moe_route(PurlinMoeContext* c, const float* logits, int tokens, int n
 
 int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const int32_t* topkIdx, const int32_t* slot,
                         int32_t* sentRow, int32_t* recvCounts, int blocks, void* stream) {
+  NvtxRange range("moeDispatch", size_t(tokens));
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.x = static_cast<const unsigned char*>(x); p.topkIdx = topkIdx; p.slot = slot; p.sentRow = sentRow; p.recvCounts = recvCounts;
@@ -397,6 +400,7 @@ int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const in
 
 int purlin_moe_combine(PurlinMoeContext* c, void* y, int tokens, const int32_t* topkIdx, const float* topkWeight,
                        const int32_t* sentRow, int blocks, void* stream) {
+  NvtxRange range("moeCombine", size_t(tokens));
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.y = static_cast<unsigned char*>(y); p.topkIdx = topkIdx; p.topkWeight = topkWeight; p.sentRow = const_cast<int32_t*>(sentRow);

@@ -25,6 +25,7 @@
 #include "purlin/constants.hpp"
 #include "purlin/plan.hpp"
 #include "purlin/signal.cuh"
+#include "purlin/telemetry.hpp"
 
 namespace purlin { void setError(const std::string& e); }
 using namespace purlin;
@@ -205,6 +206,7 @@ size_t purlin_symm_flag_bytes(int world) { return roundUp(size_t(2 * world + 4) 
 // tensor or 0; mode 1 (deterministic) never uses the switch. Epoch and error status live in the flag block.
 int purlin_symm_all_reduce(int rank, int world, const uint64_t* dataPtrs, uint64_t multicastPtr, const uint64_t* flagPtrs,
                            size_t bytes, int dtype, int reduceOp, int mode, int blocks, int mmDepth, uint64_t timeoutNs, void* stream) {
+  NvtxRange range("symmAllReduce", bytes);
   SymmParams p{};
   if (!fillParams(p, rank, world, dataPtrs, flagPtrs, bytes, mmDepth, timeoutNs)) return 1;
   if (bytes == 0) return 0;
@@ -228,6 +230,7 @@ int purlin_symm_all_reduce(int rank, int world, const uint64_t* dataPtrs, uint64
 int purlin_symm_reduce_scatter(int rank, int world, const uint64_t* dataPtrs, uint64_t multicastPtr, const uint64_t* flagPtrs,
                                void* out, size_t bytesPerRank, int dtype, int reduceOp, int mode, int blocks, int mmDepth,
                                uint64_t timeoutNs, void* stream) {
+  NvtxRange range("symmReduceScatter", bytesPerRank);
   SymmParams p{};
   if (!fillParams(p, rank, world, dataPtrs, flagPtrs, bytesPerRank, mmDepth, timeoutNs)) return 1;
   if (bytesPerRank == 0) return 0;
@@ -250,6 +253,7 @@ int purlin_symm_reduce_scatter(int rank, int world, const uint64_t* dataPtrs, ui
 // for 4 x 64 MiB), the switch sends every rank its own slice back through its link.
 int purlin_symm_all_gather(int rank, int world, const uint64_t* dataPtrs, uint64_t multicastPtr, const uint64_t* flagPtrs,
                            size_t bytesPerRank, int viaSwitch, int blocks, uint64_t timeoutNs, void* stream) {
+  NvtxRange range("symmAllGather", bytesPerRank);
   SymmParams p{};
   if (!fillParams(p, rank, world, dataPtrs, flagPtrs, bytesPerRank, 0, timeoutNs)) return 1;
   if (bytesPerRank == 0) return 0;
