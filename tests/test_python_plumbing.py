@@ -222,3 +222,22 @@ def test_strategies_example_runs_on_cpu():
     res = subprocess.run([sys.executable, os.path.join(root, "examples", "strategies.py"), "--cpu"], capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr[-2000:]
     assert "round trip exact: True" in res.stdout and "every entry 2.0" in res.stdout
+
+
+def test_plan_explainer_prints_roles_and_regions(capsys):
+    from purlin_b200 import tuning
+    from purlin_b200.utils import explain
+    tuning.clear()
+    try:
+        assert explain.main(["all_reduce", "--world", "4", "--bytes", "8K", "--gpu", ""]) == 0
+        text = capsys.readouterr().out
+        assert "latency (packets)" in text and "packet-put" in text and "packet-reduce" in text
+        assert explain.main(["all_gather", "--world", "8", "--bytes", "4M", "--gpu", ""]) == 0
+        text = capsys.readouterr().out
+        assert "throughput (staged)" in text and text.count("consume") >= 7 and "stage" in text
+        assert explain.main(["all_to_all_v", "--world", "4", "--sizes", "0,64K,1M,32", "--rank", "1", "--gpu", ""]) == 0
+        text = capsys.readouterr().out
+        assert "arrival handshake" in text and "local" in text
+        assert explain.main(["all_gather_v", "--world", "4", "--gpu", ""]) == 2      # sizes are required
+    finally:
+        tuning.clear()
