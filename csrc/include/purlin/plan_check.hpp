@@ -3,7 +3,8 @@
 // The reference has no sanitizer hooks and relies on static_asserts inside its templates (for example
 // csrc/include/purlin/snac.cuh:55-56,399-400,1181-1182). Here a plan is data, so it can be checked before it is
 // launched: user source and destination extents, the staging half, the packet slot (and its input / result halves for
-// the composed all-reduce), CTA ranges inside the grid, access alignment, chunk arithmetic. The check is host-only
+// the composed all-reduce), CTA ranges inside the grid, access alignment, chunk arithmetic, and that the steps' writes
+// tile the user's output exactly (no byte left stale, no byte with two writers). The check is host-only
 // and costs well under a microsecond per step, so planFor (host_core.cpp) runs it on every plan it hands out: the
 // GPU launcher, the CPU interpreter, the gloo executor and purlin_plan_build never see an unchecked plan. Tests
 // sweep it over worlds 2-16, sizes around every band boundary and forced policies, and corrupt plans on purpose.
@@ -20,11 +21,13 @@ namespace purlin {
 struct PlanExtents {
   size_t srcBytes = 0;       // user input of this rank
   size_t dstBytes = 0;       // user output of this rank
+  bool inPlace = false;      // src and dst are one buffer: the rank's own slice may stay where it is
 };
 
 // user buffer extents of one rank for a collective (the byte conventions of the host API)
 inline PlanExtents extentsFor(const CollectiveSpec& s) {
   PlanExtents e;
+  e.inPlace = s.inPlace;
   size_t sumIn = 0, sumOut = 0;
   for (int q = 0; q < s.world && q < kMaxRanks; ++q) { sumIn += s.sizes[q]; sumOut += s.outSizes[q]; }
   const size_t w = size_t(s.world);
@@ -43,6 +46,45 @@ inline PlanExtents extentsFor(const CollectiveSpec& s) {
 namespace detail {
 inline bool within(size_t off, size_t len, size_t limit) { return off <= limit && len <= limit - off; }
 }  // namespace detail
+
+// Every byte of the user's output must be written by exactly one step: the ranges the steps write to `dst` have to
+// tile [0, dstBytes) with neither a gap (stale output) nor an overlap (two writers racing). An in-place call may leave
+// the rank's own slice untouched, so only overlaps are errors there.
+inline std::string checkCoverage(const Plan& plan, const PlanExtents& ext) {
+  struct Range { size_t begin, end; int step; };
+  Range ranges[kMaxSteps];
+  int n = 0;
+  for (int i = 0; i < plan.nSteps; ++i) {
+    const Step& s = plan.steps[i];
+    bool writes = false;
+    switch (s.role) {
+      case kRoleLocal: case kRoleConsume: case kRoleGather: case kRolePacketGet: case kRolePacketReduce: writes = true; break;
+      case kRoleReduce: writes = (s.flags & kFlagToDst) != 0; break;
+      default: break;
+    }
+    if (writes && s.bytes) ranges[n++] = Range{size_t(s.dstOff), size_t(s.dstOff + s.bytes), i};
+  }
+  for (int a = 1; a < n; ++a)                       // insertion sort: at most kMaxSteps entries
+    for (int b = a; b > 0 && ranges[b].begin < ranges[b - 1].begin; --b) { const Range t = ranges[b]; ranges[b] = ranges[b - 1]; ranges[b - 1] = t; }
+  char buf[200];
+  size_t at = 0;
+  for (int k = 0; k < n; ++k) {
+    if (ranges[k].begin < at) {
+      std::snprintf(buf, sizeof(buf), "steps %d and %d both write the output at byte %zu", ranges[k - 1].step, ranges[k].step, ranges[k].begin);
+      return buf;
+    }
+    if (ranges[k].begin > at && !ext.inPlace) {
+      std::snprintf(buf, sizeof(buf), "no step writes the output bytes [%zu, %zu)", at, ranges[k].begin);
+      return buf;
+    }
+    at = ranges[k].end;
+  }
+  if (at < ext.dstBytes && !ext.inPlace) {
+    std::snprintf(buf, sizeof(buf), "no step writes the output bytes [%zu, %zu)", at, ext.dstBytes);
+    return buf;
+  }
+  return std::string();
+}
 
 // Returns an empty string when the plan is sound, else a description of the first violation.
 inline std::string checkPlan(const Plan& plan, int world, const WorkspaceLayout& ws, const PlanExtents& ext) {
@@ -129,7 +171,7 @@ inline std::string checkPlan(const Plan& plan, int world, const WorkspaceLayout&
         return buf;
     }
   }
-  return std::string();
+  return checkCoverage(plan, ext);
 }
 
 }  // namespace purlin

@@ -106,3 +106,30 @@ def test_corrupted_plans_are_caught():
     bad = copy.deepcopy(small)
     bad.steps[put].dstOff = 8 << 20
     assert "packet slot" in P.check_plan(bad, world, nb, nb, STAGING)
+
+
+def test_output_coverage_gaps_and_overlaps_are_caught():
+    world, n = 4, 32 * 4 * 512
+    plan, _ = P.build_plan(AG, world, 1, n, staging_size=STAGING, policy=policy())
+    ib, ob = in_out_bytes(AG, world, 1, n, None)
+    assert P.check_plan(plan, world, ib, ob, STAGING) == ""
+    consumers = [i for i in range(plan.nSteps) if plan.steps[i].role == 2]
+    assert len(consumers) == world - 1
+
+    def mutated(fn):
+        p = copy.deepcopy(plan)
+        fn(p)
+        return P.check_plan(p, world, ib, ob, STAGING)
+
+    # two consumers write the same slice: an overlap, and the slice the second one left is a gap
+    msg = mutated(lambda p: setattr(p.steps[consumers[1]], "dstOff", p.steps[consumers[0]].dstOff))
+    assert "both write the output" in msg or "no step writes" in msg
+    # a consumer that copies less than its slice leaves stale bytes behind
+    def shorten(p):
+        s = p.steps[consumers[0]]
+        s.bytes -= 32
+        s.chunkBytes = s.bytes
+    assert "no step writes the output bytes" in mutated(shorten)
+    # dropping the self copy leaves the rank's own slice unwritten
+    local = next(i for i in range(plan.nSteps) if plan.steps[i].role == 1)
+    assert "no step writes the output bytes" in mutated(lambda p: setattr(p.steps[local], "bytes", 0))
