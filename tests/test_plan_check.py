@@ -133,3 +133,38 @@ def test_output_coverage_gaps_and_overlaps_are_caught():
     # dropping the self copy leaves the rank's own slice unwritten
     local = next(i for i in range(plan.nSteps) if plan.steps[i].role == 1)
     assert "no step writes the output bytes" in mutated(lambda p: setattr(p.steps[local], "bytes", 0))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_table_driven_nvls_and_in_place_plans_pass(world):
+    """What a GPU run sees and the interpreter does not: the measured table installed, a multicast alias on offer,
+    in-place calls, both reduction modes, sizes up to 1 GiB. None may be refused by the plan check."""
+    from purlin_b200 import tuning
+    built = 0
+    try:
+        for use_table in (False, True):
+            tuning.clear()
+            if use_table:
+                assert tuning.load_for("NVIDIA B200", world) is not None
+            for coll in (AR, AG, RS, A2A):
+                for size in (32 * world, 8 << 10, 512 << 10, 4 << 20, 32 << 20, 256 << 20, 1 << 30):
+                    size = size // (32 * world) * (32 * world)
+                    for mc in (False, True):
+                        for in_place in (False, True):
+                            for mode in (P.ReductionMode.NON_DETERMINISTIC, P.ReductionMode.DETERMINISTIC):
+                                try:
+                                    P.build_plan(coll, world, world - 1, size, multicast=mc, in_place=in_place, mode=mode)
+                                    built += 1
+                                except RuntimeError as e:
+                                    assert "plan check" not in str(e), f"coll {coll} world {world} bytes {size} mc {mc} in-place {in_place}: {e}"
+            for kw in (dict(arPath=1, memType=1), dict(arPath=1, memType=1, chunkBytes=1 << 20), dict(regime=0, arPath=0, lrMulticast=1),
+                       dict(regime=0, arPath=1, lrMulticast=1)):
+                for size in (32 * world * 8, 1 << 20, 16 << 20):
+                    try:
+                        P.build_plan(AR, world, 0, size, multicast=True, policy=policy(**kw))
+                        built += 1
+                    except RuntimeError as e:
+                        assert "plan check" not in str(e), f"forced {kw} world {world} bytes {size}: {e}"
+    finally:
+        tuning.clear()
+    assert built > 300
