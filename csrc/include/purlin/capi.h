@@ -43,6 +43,13 @@ int purlin_sim_run(int collective, int world, size_t bytes, const size_t* sizesM
                    size_t stagingTRSize, const void* policy, const void* const* srcs, void* const* dsts,
                    int dropRank, uint32_t* statusOut);
 
+/* The same interpreter on a SEQUENCE of calls with no barrier between them: a rank starts its next call as soon as its
+ * own steps are done, and a seeded random scheduler moves one agent one chunk at a time. collectives / bytes /
+ * sizesMatrices (NULL entries for fixed-size forms): one entry per call; srcs / dsts: nCalls x world pointers, call-major. */
+int purlin_sim_run_overlapped(int nCalls, const int* collectives, const size_t* bytes, const size_t* const* sizesMatrices,
+                              int world, int dtype, int reduceOp, int mode, size_t stagingTRSize, const void* policy,
+                              const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, uint32_t* statusOut);
+
 /* ---- contexts ---- */
 /* peerPtrs[world]: base of every rank's symmetric workspace block (peerPtrs[rank] is local).
  * multicastPtr: NVLS alias of the same block, or 0. Honours PURLIN_DISABLE_MULTIMEM and PURLIN_DISABLE_MULTIMEM_LR. */

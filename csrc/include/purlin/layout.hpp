@@ -481,7 +481,10 @@ inline bool buildLatencyPlan(const CollectiveSpec& spec, const Policy& pol, cons
   PieceTable pt;
   WorkspaceLayout unbounded = ws; unbounded.stagingTRSize = ~size_t(0) >> 8;  // offsets here are packet offsets, not staging
   if (!pieceTable(spec, unbounded, composed ? AllReducePath::composed : AllReducePath::direct, pt, err)) return false;
-  plan.varLenArrival = 0;   // every rank waits on every peer's packets or posts none; packets carry their own flags
+  // Fixed-size forms: every rank waits on every peer's packets, which carry their own flags. Variable-length forms keep
+  // the arrival handshake here too: a rank whose partition is empty waits on no packet at all and could run two calls
+  // ahead, into the packet half a slower rank is still reading (found by the interpreter's overlapped-call schedules).
+  plan.varLenArrival = (isVariable(spec.in) || isVariable(spec.out)) ? 1 : 0;
   const size_t slotPayload = ws.packetStride / 2;           // 16-byte packets carry 8 bytes
   const size_t cap = composed ? slotPayload / 2 : slotPayload;
   detail::Builder b{plan, err};

@@ -242,6 +242,7 @@ struct Sim {
   WorkspaceLayout ws;
   std::vector<SimRank> ranks;
   uint32_t status[4] = {0, 0, 0, 0};
+  int quantum = 0;   // chunks (or batches of 64 packet words) one advance() may process; 0: as far as its waits allow
 
   unsigned char* stagingTR(int p, int half) { return ranks[p].block.data() + size_t(half) * ws.stagingTRSize; }
   HostPacket* slot(int onRank, int fromRank, int half, bool result) {
@@ -269,6 +270,7 @@ struct Sim {
     const int r = a.rank, half = int(R.seq & 1);
     const uint64_t seq = R.seq;
     bool progressed = false;
+    int did = 0;   // work units done in this invocation (bounded by `quantum` when the scheduler wants fine interleaving)
     switch (s.role) {
       case kRoleStage:
         while (a.chunk < s.chunks) {
@@ -284,6 +286,7 @@ struct Sim {
           const uint64_t v = flagValue(seq, k);
           if (s.peer >= 0) signal(s.peer, r) = v; else for (int q = 0; q < W; ++q) signal(q, r) = v;
           ++a.chunk; progressed = true;
+          if (quantum && ++did >= quantum && a.chunk < s.chunks) return true;
         }
         a.done = true; return true;
       case kRoleLocal:
@@ -299,6 +302,7 @@ struct Sim {
           splitCopy(R.dst + s.dstOff + size_t(k) * s.chunkBytes, stagingTR(from, half) + s.srcOff + slotOff(s, k), chunkLen(s, k), s.blockCount);
           if (s.flags & kFlagCyclic) consumed(s.peer, r) = flagValue(seq, k);
           ++a.chunk; progressed = true;
+          if (quantum && ++did >= quantum && a.chunk < s.chunks) return true;
         }
         a.done = true; return true;
       case kRoleReduce:
@@ -321,6 +325,7 @@ struct Sim {
             if (s.flags & kFlagCyclic) consumed(q, r) = v;
           }
           ++a.chunk; progressed = true;
+          if (quantum && ++did >= quantum && a.chunk < s.chunks) return true;
         }
         a.done = true; return true;
       case kRolePacketPut: {
@@ -341,6 +346,7 @@ struct Sim {
           if (p[a.word].flag != flag) return progressed;
           std::memcpy(R.dst + s.dstOff + a.word * 8, &p[a.word].data, 8);
           ++a.word; progressed = true;
+          if (quantum && ++did >= 64 * quantum && a.word < words) return true;
         }
         a.done = true; return true;
       }
@@ -364,6 +370,7 @@ struct Sim {
           if (s.flags & kFlagPublish)
             for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagMulticastOut)) continue; slot(q, r, half, true)[i] = HostPacket{out, flag}; }
           ++a.word; progressed = true;
+          if (quantum && ++did >= 64 * quantum && a.word < words) return true;
         }
         a.done = true; return true;
       }
@@ -418,6 +425,91 @@ struct Sim {
     for (int r = 0; r < W; ++r) if (!ranks[r].absent) ++ranks[r].seq;
     return status[0] == 0;
   }
+
+  // A sequence of calls with NO barrier between them: a rank starts its next call as soon as its own steps of the
+  // current one are done (stream order), whatever its peers are doing, and a seeded random scheduler decides which
+  // agent of which rank moves next, one chunk at a time. This is the situation the ordering invariant is about (a
+  // fast rank may be a whole call ahead of a slow one, reusing a staging half the slow one has only just released);
+  // a protocol error shows as a wrong output or as a schedule in which nobody can move.
+  struct CallData { std::vector<Plan> plans; std::vector<const unsigned char*> srcs; std::vector<unsigned char*> dsts; };
+  bool overlapped(const std::vector<CallData>& calls, uint64_t seed) {
+    const int n = int(calls.size());
+    std::vector<int> cur(W, 0);
+    std::vector<std::vector<Agent>> agents(W);
+    std::vector<char> finished(W, 0);
+    uint64_t rng = seed * 0x9e3779b97f4a7c15ull + 0x1234567ull;
+    auto next = [&]() { rng ^= rng << 13; rng ^= rng >> 7; rng ^= rng << 17; return rng; };
+    auto start = [&](int r) {
+      if (cur[r] >= n) { finished[r] = 1; agents[r].clear(); return; }
+      SimRank& R = ranks[r];
+      R.plan = calls[cur[r]].plans[r]; R.src = calls[cur[r]].srcs[r]; R.dst = calls[cur[r]].dsts[r];
+      const int half = int(R.seq & 1);
+      if (R.plan.varLenArrival) for (int q = 0; q < W; ++q) *arrival(q, half, r) = HostPacket{R.plan.payloadBytes, flagValue(R.seq, 0)};
+      agents[r].clear();
+      for (int s = 0; s < R.plan.nSteps; ++s) { Agent a; a.rank = r; a.step = s; agents[r].push_back(a); }
+    };
+    for (int r = 0; r < W; ++r) start(r);
+    for (;;) {
+      bool allFinished = true;
+      for (int r = 0; r < W; ++r) allFinished = allFinished && finished[r];
+      if (allFinished) return status[0] == 0;
+      // agents that may move: not done, and no earlier unfinished step of the same rank shares their CTAs
+      std::vector<std::pair<int, int>> cand;
+      for (int r = 0; r < W; ++r) {
+        if (finished[r]) continue;
+        for (size_t i = 0; i < agents[r].size(); ++i) {
+          if (agents[r][i].done) continue;
+          const Step& s = ranks[r].plan.steps[agents[r][i].step];
+          bool blocked = false;
+          for (size_t j = 0; j < i && !blocked; ++j) {
+            if (agents[r][j].done) continue;
+            const Step& t = ranks[r].plan.steps[agents[r][j].step];
+            blocked = t.blockBegin < s.blockBegin + s.blockCount && s.blockBegin < t.blockBegin + t.blockCount;
+          }
+          if (!blocked) cand.emplace_back(r, int(i));
+        }
+      }
+      for (size_t i = cand.size(); i > 1; --i) std::swap(cand[i - 1], cand[size_t(next() % i)]);
+      bool progress = false;
+      for (const auto& c : cand)
+        if (advance(agents[c.first][size_t(c.second)])) { progress = true; break; }   // one agent per turn
+      if (status[0]) return false;
+      // a rank whose steps are all done finishes its call (after the arrival handshake of a variable-length form)
+      for (int r = 0; r < W; ++r) {
+        if (finished[r]) continue;
+        bool done = true;
+        for (const Agent& a : agents[r]) done = done && a.done;
+        if (!done) continue;
+        SimRank& R = ranks[r];
+        if (R.plan.varLenArrival) {
+          const int half = int(R.seq & 1);
+          bool arrived = true;
+          for (int q = 0; q < W; ++q) arrived = arrived && arrival(r, half, q)->flag == flagValue(R.seq, 0);
+          if (!arrived) continue;
+        }
+        ++R.seq; ++cur[r];
+        start(r);
+        progress = true;
+      }
+      if (!progress) {
+        if (std::getenv("PURLIN_SIM_DEBUG"))
+          for (int r = 0; r < W; ++r) {
+            std::fprintf(stderr, "rank %d call %d seq %llu finished %d:", r, cur[r], (unsigned long long)ranks[r].seq, int(finished[r]));
+            for (const Agent& a : agents[r]) if (!a.done) { const Step& s = ranks[r].plan.steps[a.step]; std::fprintf(stderr, " [step %d role %d peer %d chunk %u word %zu bytes %llu]", a.step, s.role, s.peer, a.chunk, a.word, (unsigned long long)s.bytes); }
+            std::fprintf(stderr, "\n");
+          }
+        for (int r = 0; r < W && !status[0]; ++r)
+          for (const Agent& a : agents[r]) if (!a.done) {
+            const Step& s = ranks[r].plan.steps[a.step];
+            status[0] = (s.role >= kRolePacketPut) ? kStatusTimeoutPacket : kStatusTimeoutSignal;
+            status[1] = uint32_t(a.step); status[2] = uint32_t(s.peer); status[3] = a.chunk;
+            break;
+          }
+        if (!status[0]) { status[0] = kStatusTimeoutArrival; }
+        return false;
+      }
+    }
+  }
 };
 
 }  // namespace
@@ -449,5 +541,40 @@ extern "C" int purlin_sim_run(int collective, int world, size_t bytes, const siz
   for (int rep = 0; rep < 2 && ok; ++rep) ok = sim.call();
   if (statusOut) std::memcpy(statusOut, sim.status, sizeof(sim.status));
   if (!ok && sim.status[0] == 0) sim.status[0] = kStatusTimeoutSignal;
+  return 0;
+}
+
+// A sequence of `nCalls` collectives on one set of workspaces with no barrier between calls and a seeded random
+// scheduler (see Sim::overlapped). collectives[c], bytes[c], sizesMatrices[c] (null for fixed-size forms) describe call
+// c; srcs / dsts hold nCalls x world pointers, call-major. quantum: chunks one scheduling turn may process (1 = finest).
+extern "C" int purlin_sim_run_overlapped(int nCalls, const int* collectives, const size_t* bytes, const size_t* const* sizesMatrices,
+                                         int world, int dtype, int reduceOp, int mode, size_t stagingTRSize, const void* policy,
+                                         const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, uint32_t* statusOut) {
+  if (world < 1 || world > kMaxRanks || nCalls < 1) { setError("invalid world size or call count"); return 1; }
+  Sim sim;
+  sim.W = world;
+  sim.ws = workspaceLayout(world, stagingTRSize);
+  sim.quantum = quantum;
+  sim.ranks.resize(world);
+  for (int r = 0; r < world; ++r) sim.ranks[r].block.assign(sim.ws.totalBytes, 0);
+  std::vector<Sim::CallData> calls(static_cast<size_t>(nCalls));
+  for (int c = 0; c < nCalls; ++c) {
+    Sim::CallData& cd = calls[size_t(c)];
+    cd.plans.resize(world); cd.srcs.resize(world); cd.dsts.resize(world);
+    const size_t* matrix = sizesMatrices ? sizesMatrices[c] : nullptr;
+    const bool a2av = collectives[c] == int(CollectiveType::allToAllV);
+    for (int r = 0; r < world; ++r) {
+      cd.srcs[r] = static_cast<const unsigned char*>(srcs[size_t(c) * world + r]);
+      cd.dsts[r] = static_cast<unsigned char*>(dsts[size_t(c) * world + r]);
+      size_t in[kMaxRanks] = {}, out[kMaxRanks] = {};
+      if (matrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? matrix[size_t(r) * world + q] : matrix[q]; out[q] = a2av ? matrix[size_t(q) * world + r] : 0; }
+      CollectiveSpec s;
+      if (!makeSpec(s, collectives[c], world, r, bytes[c], matrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, cd.srcs[r] == cd.dsts[r])) return 1;
+      if (!planFor(s, sim.ws, static_cast<const Policy*>(policy), cd.plans[r], nullptr)) return 1;
+    }
+  }
+  const bool ok = sim.overlapped(calls, seed);
+  if (statusOut) std::memcpy(statusOut, sim.status, sizeof(sim.status));
+  if (!ok && sim.status[0] == 0 && statusOut) statusOut[0] = kStatusTimeoutSignal;
   return 0;
 }

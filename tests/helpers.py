@@ -96,6 +96,43 @@ def sim(coll, world, nbytes=0, sizes=None, dtype=4, op=0, staging=1 << 20, polic
     return list(status), outs, exp
 
 
+def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed=0, quantum=1):
+    """Runs a list of calls [(collective, nbytes, sizes), ...] through the interpreter with no barrier between calls and a
+    seeded random schedule; returns (status, outputs[call][rank], expected[call][rank])."""
+    lib = _native.host()
+    lib.purlin_sim_run_overlapped.argtypes = [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_void_p), C.c_int, C.c_int,
+                                              C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                                              C.c_uint64, C.c_int, C.POINTER(C.c_uint32)]
+    e = ELEM[dtype]
+    n = len(calls)
+    ins, outs, keep = [], [], []
+    for c, (coll, nbytes, sizes) in enumerate(calls):
+        row_in, row_out = [], []
+        for r in range(world):
+            ib, ob = in_out_bytes(coll, world, r, nbytes, sizes)
+            row_in.append(ints(ib // e, dtype, seed * 7919 + c * 101 + r))
+            row_out.append(torch.full((max(ob // e, 1),), 7, dtype=torch.float32).to(TORCH_DT[dtype])[: ob // e].clone())
+        ins.append(row_in)
+        outs.append(row_out)
+    colls = (C.c_int * n)(*[c[0] for c in calls])
+    nb = (C.c_size_t * n)(*[c[1] for c in calls])
+    mats = []
+    for coll, _, sizes in calls:
+        m = flat_sizes(coll, world, sizes)
+        keep.append(m)
+        mats.append(C.cast(m, C.c_void_p) if m is not None else None)
+    mat_arr = (C.c_void_p * n)(*mats)
+    srcs = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in ins for t in row])
+    dsts = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in outs for t in row])
+    status = (C.c_uint32 * 4)()
+    rc = lib.purlin_sim_run_overlapped(n, colls, nb, mat_arr, world, dtype, op, 0, staging,
+                                       C.byref(policy) if policy is not None else None, srcs, dsts, seed, quantum, status)
+    if rc != 0:
+        raise RuntimeError(_native.last_error(lib))
+    exp = [[expected(coll, world, r, ins[c], nbytes, sizes, dtype, op) for r in range(world)] for c, (coll, nbytes, sizes) in enumerate(calls)]
+    return list(status), outs, exp
+
+
 def policy(**kw):
     p = _native.Policy()
     base = dict(regime=1, threads=256, putBlocks=4, localBlocks=2, consumeBlocks=8, gatherBlocks=8, lrBlocks=2, memType=0,
