@@ -48,7 +48,8 @@ int purlin_sim_run(int collective, int world, size_t bytes, const size_t* sizesM
  * sizesMatrices (NULL entries for fixed-size forms): one entry per call; srcs / dsts: nCalls x world pointers, call-major. */
 int purlin_sim_run_overlapped(int nCalls, const int* collectives, const size_t* bytes, const size_t* const* sizesMatrices,
                               int world, int dtype, int reduceOp, int mode, size_t stagingTRSize, const void* policy,
-                              const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, uint32_t* statusOut);
+                              const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, int multicastAvailable,
+                              uint32_t* statusOut);
 
 /* ---- contexts ---- */
 /* peerPtrs[world]: base of every rank's symmetric workspace block (peerPtrs[rank] is local).

@@ -549,7 +549,8 @@ extern "C" int purlin_sim_run(int collective, int world, size_t bytes, const siz
 // c; srcs / dsts hold nCalls x world pointers, call-major. quantum: chunks one scheduling turn may process (1 = finest).
 extern "C" int purlin_sim_run_overlapped(int nCalls, const int* collectives, const size_t* bytes, const size_t* const* sizesMatrices,
                                          int world, int dtype, int reduceOp, int mode, size_t stagingTRSize, const void* policy,
-                                         const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, uint32_t* statusOut) {
+                                         const void* const* srcs, void* const* dsts, uint64_t seed, int quantum, int multicastAvailable,
+                                         uint32_t* statusOut) {
   if (world < 1 || world > kMaxRanks || nCalls < 1) { setError("invalid world size or call count"); return 1; }
   Sim sim;
   sim.W = world;
@@ -569,7 +570,10 @@ extern "C" int purlin_sim_run_overlapped(int nCalls, const int* collectives, con
       size_t in[kMaxRanks] = {}, out[kMaxRanks] = {};
       if (matrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? matrix[size_t(r) * world + q] : matrix[q]; out[q] = a2av ? matrix[size_t(q) * world + r] : 0; }
       CollectiveSpec s;
-      if (!makeSpec(s, collectives[c], world, r, bytes[c], matrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, cd.srcs[r] == cd.dsts[r])) return 1;
+      // with a multicast alias on offer the plans may use the switch variants: the interpreter models multimem.ld_reduce
+      // as a read of every rank's staging and multimem.st as a write to every rank's
+      if (!makeSpec(s, collectives[c], world, r, bytes[c], matrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode,
+                    multicastAvailable, cd.srcs[r] == cd.dsts[r])) return 1;
       if (!planFor(s, sim.ws, static_cast<const Policy*>(policy), cd.plans[r], nullptr)) return 1;
     }
   }

@@ -96,13 +96,13 @@ def sim(coll, world, nbytes=0, sizes=None, dtype=4, op=0, staging=1 << 20, polic
     return list(status), outs, exp
 
 
-def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed=0, quantum=1):
+def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed=0, quantum=1, multicast=False):
     """Runs a list of calls [(collective, nbytes, sizes), ...] through the interpreter with no barrier between calls and a
     seeded random schedule; returns (status, outputs[call][rank], expected[call][rank])."""
     lib = _native.host()
     lib.purlin_sim_run_overlapped.argtypes = [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                               C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
-                                              C.c_uint64, C.c_int, C.POINTER(C.c_uint32)]
+                                              C.c_uint64, C.c_int, C.c_int, C.POINTER(C.c_uint32)]
     e = ELEM[dtype]
     n = len(calls)
     ins, outs, keep = [], [], []
@@ -126,7 +126,7 @@ def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed
     dsts = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in outs for t in row])
     status = (C.c_uint32 * 4)()
     rc = lib.purlin_sim_run_overlapped(n, colls, nb, mat_arr, world, dtype, op, 0, staging,
-                                       C.byref(policy) if policy is not None else None, srcs, dsts, seed, quantum, status)
+                                       C.byref(policy) if policy is not None else None, srcs, dsts, seed, quantum, int(multicast), status)
     if rc != 0:
         raise RuntimeError(_native.last_error(lib))
     exp = [[expected(coll, world, r, ins[c], nbytes, sizes, dtype, op) for r in range(world)] for c, (coll, nbytes, sizes) in enumerate(calls)]

@@ -80,3 +80,16 @@ def test_coarse_and_fine_schedules_agree():
     calls = [(AR, 32 * world * 300, None), (AG, 32 * 300, None), (RS, 32 * 300, None)] * 2
     for quantum in (1, 3, 0):
         _check(calls, world, seed=5, dtype=0, quantum=quantum, policy=policy(chunkBytes=8192))
+
+
+@pytest.mark.parametrize("kw", [dict(arPath=1, memType=1), dict(arPath=1, memType=1, chunkBytes=8192), dict(regime=0, arPath=0, lrMulticast=1),
+                                dict(regime=0, arPath=1, lrMulticast=1)])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_switch_variants_back_to_back(kw, world):
+    """The NVLS plans (in-switch reduction, results broadcast into every rank's staging or packet slots, gathered from the
+    rank's own memory) under the same overlapped schedules: the interpreter models multimem.ld_reduce as a read of every
+    rank's staging and multimem.st as a write to every rank's."""
+    n = 32 * world * 48
+    calls = [(AR, n, None), (AR, n, None), (AG, n // world, None), (AR, n, None), (RS, n // world, None), (AR, n, None)]
+    for seed in (41, 42, 43):
+        _check(calls, world, seed=seed, dtype=0, policy=policy(**kw), multicast=True)
