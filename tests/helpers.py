@@ -96,9 +96,10 @@ def sim(coll, world, nbytes=0, sizes=None, dtype=4, op=0, staging=1 << 20, polic
     return list(status), outs, exp
 
 
-def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed=0, quantum=1, multicast=False):
+def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed=0, quantum=1, multicast=False, in_place_ar=False):
     """Runs a list of calls [(collective, nbytes, sizes), ...] through the interpreter with no barrier between calls and a
-    seeded random schedule; returns (status, outputs[call][rank], expected[call][rank])."""
+    seeded random schedule; returns (status, outputs[call][rank], expected[call][rank]). ``in_place_ar``: all-reduce calls
+    get one buffer as source and destination."""
     lib = _native.host()
     lib.purlin_sim_run_overlapped.argtypes = [C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_size_t), C.POINTER(C.c_void_p), C.c_int, C.c_int,
                                               C.c_int, C.c_int, C.c_size_t, C.c_void_p, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
@@ -111,7 +112,10 @@ def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed
         for r in range(world):
             ib, ob = in_out_bytes(coll, world, r, nbytes, sizes)
             row_in.append(ints(ib // e, dtype, seed * 7919 + c * 101 + r))
-            row_out.append(torch.full((max(ob // e, 1),), 7, dtype=torch.float32).to(TORCH_DT[dtype])[: ob // e].clone())
+            if in_place_ar and coll == AR:
+                row_out.append(row_in[-1].clone())      # the work buffer: input now, result afterwards
+            else:
+                row_out.append(torch.full((max(ob // e, 1),), 7, dtype=torch.float32).to(TORCH_DT[dtype])[: ob // e].clone())
         ins.append(row_in)
         outs.append(row_out)
     colls = (C.c_int * n)(*[c[0] for c in calls])
@@ -122,7 +126,8 @@ def sim_sequence(calls, world, dtype=4, op=0, staging=1 << 20, policy=None, seed
         keep.append(m)
         mats.append(C.cast(m, C.c_void_p) if m is not None else None)
     mat_arr = (C.c_void_p * n)(*mats)
-    srcs = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in ins for t in row])
+    src_rows = [outs[c] if (in_place_ar and calls[c][0] == AR) else ins[c] for c in range(n)]
+    srcs = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in src_rows for t in row])
     dsts = (C.c_void_p * (n * world))(*[t.data_ptr() if t.numel() else None for row in outs for t in row])
     status = (C.c_uint32 * 4)()
     rc = lib.purlin_sim_run_overlapped(n, colls, nb, mat_arr, world, dtype, op, 0, staging,

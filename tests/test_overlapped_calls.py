@@ -93,3 +93,13 @@ def test_switch_variants_back_to_back(kw, world):
     calls = [(AR, n, None), (AR, n, None), (AG, n // world, None), (AR, n, None), (RS, n // world, None), (AR, n, None)]
     for seed in (41, 42, 43):
         _check(calls, world, seed=seed, dtype=0, policy=policy(**kw), multicast=True)
+
+
+@pytest.mark.parametrize("kw", [dict(), dict(arPath=0), dict(regime=0, arPath=0), dict(regime=0, arPath=1), dict(chunkBytes=4096)])
+@pytest.mark.parametrize("world", [2, 4])
+def test_in_place_all_reduce_back_to_back(kw, world):
+    # source and destination are one buffer: a rank's result must not reach the buffer before every peer has taken its input
+    n = 32 * world * 40
+    calls = [(AR, n, None), (AG, n // world, None), (AR, n, None), (AR, n, None)]
+    for seed in (51, 52, 53):
+        _check(calls, world, seed=seed, dtype=4, policy=policy(**kw) if kw else None, in_place_ar=True)
