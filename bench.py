@@ -37,6 +37,77 @@ def _peaks():
         return 1400.0, 1590.0, "fallback"
 
 
+class ClockSampler:
+    """Reads SM clocks and throttle reasons through NVML (read-only) on a thread while a timed region runs.
+
+    It lives in this file so that the reference arm imports nothing of this repository's package. One sampler can
+    bracket several regions (``with sampler: ...`` more than once); the samples accumulate.
+    """
+
+    def __init__(self, index=0, period_s=0.001):
+        import threading
+        self.samples, self.reasons, self.max_mhz = [], set(), 0
+        self.period = period_s
+        self._stop, self._thread, self._threading = threading.Event(), None, threading
+        self._nvml = self._handle = None
+        self._names = {}
+        try:
+            import pynvml
+            import torch
+            pynvml.nvmlInit()
+            try:
+                uuid = str(torch.cuda.get_device_properties(index).uuid)
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(uuid if uuid.startswith("GPU-") else "GPU-" + uuid)
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM)
+            self._names = {
+                pynvml.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+                pynvml.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+                pynvml.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+                pynvml.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            }
+            self._sample()          # warms the NVML calls; dropped
+            self.samples.clear()
+            self.reasons.clear()
+        except Exception as e:
+            self._nvml = None
+            self.reasons.add(f"nvml_unavailable:{type(e).__name__}")
+
+    def _sample(self):
+        self.samples.append(self._nvml.nvmlDeviceGetClockInfo(self._handle, self._nvml.NVML_CLOCK_SM))
+        r = self._nvml.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle)
+        for bit, n in self._names.items():
+            if r & bit:
+                self.reasons.add(n)
+
+    def _run(self):
+        try:
+            while not self._stop.is_set():
+                self._sample()
+                self._stop.wait(self.period)
+        except Exception as e:
+            self.reasons.add(f"nvml_error:{type(e).__name__}")
+
+    def __enter__(self):
+        if self._nvml is not None:
+            self._stop.clear()
+            self._thread = self._threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(2.0)
+            self._thread = None
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else 0, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
 def run_reference(args):
     """The same metric on the unmodified reference: its Python API (purlin.initialize / all_gather / reduce_scatter from
     baseline/_ref) around cuBLAS GEMMs, which is how a user of the reference runs this block, since the reference has no
@@ -67,9 +138,6 @@ def run_reference(args):
                            "pybind11), which needs a network; the offline build (baseline/build_reference_module.py) has not been run")
     if world == 1:
         return unavailable("at one GPU the block has no collective, so nothing of the reference would run (it has no GEMM)")
-    if os.environ.get("PURLIN_REFERENCE_ARM") != "1":
-        return unavailable("the reference's binding is built (offline, from its own sources) and loads, but its multi-GPU kernels wait "
-                           "without a time limit and have not yet run under supervision on this pool; PURLIN_REFERENCE_ARM=1 runs the arm")
     try:
         os.environ["PURLIN_CACHE_DIR"] = cache
         _reference_arm(args, reference, rank, world)
@@ -81,7 +149,6 @@ def _reference_arm(args, reference, rank, world):
     """All-gather (reference) -> gate/up GEMMs + SwiGLU (torch) -> down GEMM (torch) -> reduce-scatter (reference)."""
     import torch
     import torch.distributed as dist
-    from purlin_b200.utils.bench import ClockSampler     # NVML reader only; nothing of this package is on the timed path
     local = int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -208,7 +275,6 @@ def main():
     import torch.distributed as dist
     import purlin_b200 as purlin
     from purlin_b200.models.tp_mlp import TensorParallelMLP
-    from purlin_b200.utils.bench import ClockSampler
 
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
