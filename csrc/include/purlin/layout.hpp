@@ -182,14 +182,20 @@ inline void chunkStream(Step& s, size_t chunkBytes, size_t windowBytes) {
   c = std::max<size_t>(roundUp(c, kAccessAlign), kAccessAlign);
   // flags reserve 2^20 values per call
   while (ceilDiv(s.bytes, c) >= (1u << kSeqShift)) c *= 2;
-  s.chunkBytes = c;
-  s.chunks = uint32_t(ceilDiv(s.bytes, c));
-  const size_t fit = std::max<size_t>(windowBytes / c, 1);
-  if (s.chunks > fit) {
-    s.slots = uint32_t(std::min<size_t>(fit, kMaxChunks));
-    s.flags |= kFlagCyclic;
-  } else {
-    s.slots = s.chunks;
+  for (;;) {
+    s.chunkBytes = c;
+    s.chunks = uint32_t(ceilDiv(s.bytes, c));
+    const size_t fit = std::max<size_t>(windowBytes / c, 1);
+    if (s.chunks > fit) {
+      s.slots = uint32_t(std::min<size_t>(fit, kMaxChunks));
+      s.flags |= kFlagCyclic;
+      return;
+    }
+    // A resident stream has no back-pressure between the CTAs of a step, and its last-arrival counters are indexed
+    // k mod kMaxChunks: more chunks than counters would let a CTA that runs ahead share a counter with a chunk still
+    // in use. A caller-forced tiny chunk is therefore raised until the stream has at most kMaxChunks chunks.
+    if (s.chunks <= uint32_t(kMaxChunks)) { s.slots = s.chunks; return; }
+    c = roundUp(c * 2, kAccessAlign);
   }
 }
 

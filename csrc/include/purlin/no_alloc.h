@@ -10,7 +10,7 @@
  * library until the process exits. The caller passes nothing but inputs and outputs.
  *
  * Rules of use:
- *   - experts must be a multiple of 32 and at most PURLIN_NOALLOC_MAX_EXPERTS; topk 1..8. Anything larger is refused
+ *   - experts must be 32, 64, 128, 256 or 512 (PURLIN_NOALLOC_MAX_EXPERTS); topk 1..8. Anything else is refused
  *     with an error (purlin_last_error()), not truncated.
  *   - The first call on each device resolves the device address of the scratch array (cudaGetSymbolAddress) with that
  *     device current. Make that first call before any stream capture begins.

@@ -290,7 +290,7 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
   if (!h) { setError("null context"); return 1; }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   CollectiveSpec spec;
-  if (!makeSpec(spec, collective, h->dev.world, h->dev.rank, bytes, sizes, outSizes, dtype, reduceOp, mode, h->hasMulticast, src == dst)) return 1;
+  if (!makeSpec(spec, collective, h->dev.world, h->dev.rank, bytes, sizes, outSizes, dtype, reduceOp, mode, h->hasMulticast, src == dst && src != nullptr)) return 1;
   if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) % 16) { setError("buffers must be 16-byte aligned (32 for full speed)"); return 1; }
   NvtxRange range(collectiveName(collective), isVariable(spec.in) ? dispatchBytes(spec) : bytes);
   if (h->dev.world == 1) return worldOneCopy(spec, src, dst, s);
@@ -314,7 +314,7 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
     // the layout engine is deterministic in these inputs: build each plan once
     if (h->planCacheTableSize != TuningTable::global().size()) { h->planCache.clear(); h->planCacheTableSize = TuningTable::global().size(); }
     const uint64_t key = (uint64_t(bytes) << 16) ^ (uint64_t(collective) << 12) ^ (uint64_t(dtype) << 8) ^ (uint64_t(reduceOp) << 4) ^
-                         (uint64_t(mode) << 1) ^ uint64_t(src == dst);
+                         (uint64_t(mode) << 1) ^ uint64_t(src == dst && src != nullptr);
     auto it = h->planCache.find(key);
     if (it == h->planCache.end()) {
       Plan fresh;
@@ -363,7 +363,7 @@ int purlin_emu_collective(PurlinHostContext* const* ctxs, int world, int collect
     size_t in[kMaxRanks] = {}, out[kMaxRanks] = {};
     if (sizesMatrix) for (int q = 0; q < world; ++q) { in[q] = a2av ? sizesMatrix[size_t(r) * world + q] : sizesMatrix[q]; out[q] = a2av ? sizesMatrix[size_t(q) * world + r] : 0; }
     CollectiveSpec spec;
-    if (!makeSpec(spec, collective, world, r, bytes, sizesMatrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, srcs[r] == dsts[r])) return 1;
+    if (!makeSpec(spec, collective, world, r, bytes, sizesMatrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode, 0, srcs[r] == dsts[r] && srcs[r] != nullptr)) return 1;
     Policy fitted;
     const Policy* use = static_cast<const Policy*>(policy);
     if (!use) {

@@ -17,6 +17,7 @@
 
 #include "purlin/capi.h"
 #include "purlin/layout.hpp"
+#include "purlin/moe_route.cuh"
 #include "purlin/plan_check.hpp"
 #include "purlin/tuning.hpp"
 
@@ -37,6 +38,15 @@ bool fillSpec(CollectiveSpec& s, int collective, int world, int rank, size_t byt
   s.dtype = DType(dtype); s.reduceOp = ReduceOp(reduceOp); s.mode = ReductionMode(mode);
   s.multicastAvailable = multicastAvailable != 0; s.inPlace = inPlace != 0;
   if (world < 1 || world > kMaxRanks) { setError("world size must be 1..16"); return false; }
+  // In place (src == dst) is sound only where no step overwrites input another step still has to read: the all-reduce
+  // orderings and the all-gather whose own slice already sits in position. A reduce-scatter writes dst[0, n), which is
+  // the unread input slice of rank 0 on every other rank; an all-to-all writes slice q as soon as q's data arrives,
+  // possibly before this rank has staged its own slice q.
+  if (s.inPlace && world > 1 && (s.type == CollectiveType::reduceScatter || s.type == CollectiveType::reduceScatterV ||
+                                 s.type == CollectiveType::allToAll || s.type == CollectiveType::allToAllV)) {
+    setError("reduce-scatter and all-to-all cannot run in place (src == dst): use a separate output buffer");
+    return false;
+  }
   const bool v = isVariable(s.in);
   if (v) {
     if (!sizes) { setError("variable-length collective needs a size list"); return false; }
@@ -151,6 +161,16 @@ int purlin_tuning_add(int collective, int world, uint64_t maxBytes, const void* 
   return 0;
 }
 size_t purlin_tuning_size(void) { return TuningTable::global().size(); }
+
+// MoE routing of `tokens` rows on the host: the arithmetic of the routing kernels (moe_route.cuh), total for any input.
+int purlin_moe_route_host(const float* logits, int tokens, int experts, int topk, int normalize, int32_t* topkIdx, float* topkWeight) {
+  if (!logits || !topkIdx || !topkWeight || tokens < 0 || experts < 1 || experts > 1024 || topk < 1 || topk > experts) {
+    setError("route (host): experts must be 1..1024 and top-k 1..experts"); return 1;
+  }
+  for (int t = 0; t < tokens; ++t)
+    moe::routeRowHost(logits + size_t(t) * experts, experts, topk, normalize, topkIdx + size_t(t) * topk, topkWeight + size_t(t) * topk);
+  return 0;
+}
 
 }  // extern "C"
 
@@ -573,7 +593,7 @@ extern "C" int purlin_sim_run_overlapped(int nCalls, const int* collectives, con
       // with a multicast alias on offer the plans may use the switch variants: the interpreter models multimem.ld_reduce
       // as a read of every rank's staging and multimem.st as a write to every rank's
       if (!makeSpec(s, collectives[c], world, r, bytes[c], matrix ? in : nullptr, a2av ? out : nullptr, dtype, reduceOp, mode,
-                    multicastAvailable, cd.srcs[r] == cd.dsts[r])) return 1;
+                    multicastAvailable, cd.srcs[r] == cd.dsts[r] && cd.srcs[r] != nullptr)) return 1;
       if (!planFor(s, sim.ws, static_cast<const Policy*>(policy), cd.plans[r], nullptr)) return 1;
     }
   }

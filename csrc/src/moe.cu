@@ -23,6 +23,7 @@
 #include "purlin/atom.cuh"
 #include "purlin/constants.hpp"
 #include "purlin/moe.h"
+#include "purlin/moe_route.cuh"
 #include "purlin/signal.cuh"
 #include "purlin/telemetry.hpp"
 
@@ -94,40 +95,11 @@ __global__ void __launch_bounds__(kThreads) routeKernel(const float* logits, int
                                                         int32_t* topkIdx, float* topkWeight, int32_t* slot, uint32_t* counts) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= tokens) return;
-  float v[VPL];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) { v[i] = logits[size_t(warp) * experts + i * 32 + lane]; mx = fmaxf(mx, v[i]); }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) { v[i] = __expf(v[i] - mx); sum += v[i]; }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const float inv = 1.f / sum;
-  float picked = 0.f;
-  float myW = 0.f; int myE = -1;     // lane k keeps the k-th choice
-  for (int k = 0; k < topk; ++k) {
-    float best = -1.f; int bestIdx = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) if (v[i] > best) { best = v[i]; bestIdx = i * 32 + lane; }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bestIdx, o);
-      if (ob > best || (ob == best && oi < bestIdx)) { best = ob; bestIdx = oi; }   // ties go to the lower expert id
-    }
-    if ((bestIdx & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < VPL; ++i) if (i == (bestIdx >> 5)) v[i] = -1.f;
-    }
-    picked += best * inv;
-    if (lane == k) { myW = best * inv; myE = bestIdx; }
-  }
+  int myE; float myW;     // lane k keeps the k-th choice; always a valid expert id (see moe_route.cuh)
+  moe::routeToken<VPL>(logits + size_t(warp) * experts, experts, topk, normalize, lane, myE, myW);
   if (lane < topk) {
     topkIdx[size_t(warp) * topk + lane] = myE;
-    topkWeight[size_t(warp) * topk + lane] = normalize ? myW / picked : myW;
+    topkWeight[size_t(warp) * topk + lane] = myW;
     slot[size_t(warp) * topk + lane] = int32_t(atomicAdd(counts + myE, 1u));
   }
 }
@@ -160,7 +132,14 @@ __global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_const
       for (int s = 0; s < p.world; ++s) base += int(all[size_t(s) * p.experts + e2]);
     for (int s = 0; s < p.rank; ++s) base += int(all[size_t(s) * p.experts + e]);
     rowBase[e] = base;
-    if (base + int(p.localCounts[e]) > p.capacityRows) overflow = 1;
+  }
+  // Capacity is judged on the whole count matrix, which every rank holds: if any destination would receive more rows
+  // than its buffer has, every rank sees it, every rank reports it and nobody stores a row.
+  if (ok && tid < p.world) {
+    long total = 0;
+    for (int e = tid * p.expertsPerRank; e < (tid + 1) * p.expertsPerRank; ++e)
+      for (int s = 0; s < p.world; ++s) total += long(all[size_t(s) * p.experts + e]);
+    if (total > long(p.capacityRows)) overflow = 1;
   }
   if (blockIdx.x == 0 && ok) {
     // what this rank receives: rows per local expert and their total
@@ -181,6 +160,7 @@ __global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_const
     // a rank never published its counts: nothing can be placed; the status word already says why
   } else if (overflow) {
     if (tid == 0 && atomicCAS(p.status, 0u, uint32_t(kStatusBadPlan)) == 0u) { p.status[1] = 2; __threadfence(); }
+    if (blockIdx.x == 0) for (int e = tid; e <= p.expertsPerRank; e += blockDim.x) p.recvCounts[e] = 0;     // nothing was delivered
   } else {
     // 4. one warp per (token, choice): the row goes straight to its permuted place in the receiver's memory
     const int warp = tid >> 5, lane = tid & 31, warpsPerCta = blockDim.x >> 5;
@@ -189,6 +169,10 @@ __global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_const
     for (int item = blockIdx.x * warpsPerCta + warp; item < items; item += gridDim.x * warpsPerCta) {
       const int t = item / p.topk;
       const int e = p.topkIdx[item];
+      if (e < 0 || e >= p.experts) {     // an id the caller supplied out of range: report it, store nothing
+        if (lane == 0 && atomicCAS(p.status, 0u, uint32_t(kStatusBadPlan)) == 0u) { p.status[1] = 7; p.status[2] = uint32_t(item); __threadfence(); }
+        continue;
+      }
       const int dst = e / p.expertsPerRank;
       const int row = rowBase[e] + p.slot[item];
       if (lane == 0) p.sentRow[item] = row;
@@ -243,8 +227,11 @@ __global__ void __launch_bounds__(kThreads, 1) combineKernel(const __grid_consta
       for (int k = 0; k < TOPK; ++k) {
         const int item = t * TOPK + k;
         const int e = p.topkIdx[item];
-        rows[k] = p.outBuf[e / p.expertsPerRank] + size_t(p.sentRow[item]) * p.hiddenBytes;
-        w[k] = p.topkWeight[item];
+        const int r = p.sentRow[item];
+        const bool valid = e >= 0 && e < p.experts && r >= 0 && r < p.capacityRows;
+        if (!valid && lane == 0 && atomicCAS(p.status, 0u, uint32_t(kStatusBadPlan)) == 0u) { p.status[1] = 8; p.status[2] = uint32_t(item); __threadfence(); }
+        rows[k] = p.outBuf[valid ? e / p.expertsPerRank : p.rank] + size_t(valid ? r : 0) * p.hiddenBytes;
+        w[k] = valid ? p.topkWeight[item] : 0.f;
       }
       unsigned char* out = p.y + size_t(t) * p.hiddenBytes;
       for (int i = lane; i < vecs; i += 32) {
@@ -369,7 +356,8 @@ void* purlin_moe_out_buffer(PurlinMoeContext* c) { return c->peers[c->rank] + c-
 int purlin_moe_route(PurlinMoeContext* c, const float* logits, int tokens, int normalize, int32_t* topkIdx, float* topkWeight,
                      int32_t* slot, void* stream) {
   NvtxRange range("moeRoute", size_t(tokens));
-  if (tokens > c->maxTokens) { setError("more tokens than the context was created for"); return 1; }
+  if (tokens < 0 || tokens > c->maxTokens || tokens > (1 << 26)) { setError("route: more tokens than the context was created for"); return 1; }
+  if (tokens == 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   uint32_t* counts = reinterpret_cast<uint32_t*>(static_cast<unsigned char*>(c->local) + 1024);
   cudaMemsetAsync(counts, 0, size_t(c->experts) * 4, s);
@@ -388,6 +376,7 @@ int purlin_moe_route(PurlinMoeContext* c, const float* logits, int tokens, int n
 int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const int32_t* topkIdx, const int32_t* slot,
                         int32_t* sentRow, int32_t* recvCounts, int blocks, void* stream) {
   NvtxRange range("moeDispatch", size_t(tokens));
+  if (tokens < 0 || tokens > c->maxTokens) { setError("dispatch: more tokens than the context was created for"); return 1; }
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.x = static_cast<const unsigned char*>(x); p.topkIdx = topkIdx; p.slot = slot; p.sentRow = sentRow; p.recvCounts = recvCounts;
@@ -401,6 +390,7 @@ int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const in
 int purlin_moe_combine(PurlinMoeContext* c, void* y, int tokens, const int32_t* topkIdx, const float* topkWeight,
                        const int32_t* sentRow, int blocks, void* stream) {
   NvtxRange range("moeCombine", size_t(tokens));
+  if (tokens < 0 || tokens > c->maxTokens) { setError("combine: more tokens than the context was created for"); return 1; }
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.y = static_cast<unsigned char*>(y); p.topkIdx = topkIdx; p.topkWeight = topkWeight; p.sentRow = const_cast<int32_t*>(sentRow);

@@ -5,6 +5,7 @@
 #include <mutex>
 #include <string>
 
+#include "purlin/moe_route.cuh"
 #include "purlin/no_alloc.h"
 
 namespace purlin { void setError(const std::string& e); }
@@ -17,47 +18,17 @@ constexpr int kMaxDevices = 64;
 // The scratch itself. In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
 static __device__ __align__(256) uint32_t g_routeCounters[PURLIN_NOALLOC_MAX_EXPERTS];
 
-// one warp per token; the same arithmetic as the context-based routing kernel
+// one warp per token; the selection itself is the code the context-based routing kernel runs (moe_route.cuh)
 template <int VPL>   // values per lane = experts / 32
 __global__ void __launch_bounds__(kThreads) routeNoAllocKernel(const float* logits, int tokens, int experts, int topk, int normalize,
                                                                int32_t* topkIdx, float* topkWeight, int32_t* slot, uint32_t* counters) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   if (warp >= tokens) return;
-  float v[VPL];
-  float mx = -INFINITY;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) { v[i] = logits[size_t(warp) * experts + i * 32 + lane]; mx = fmaxf(mx, v[i]); }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < VPL; ++i) { v[i] = __expf(v[i] - mx); sum += v[i]; }
-#pragma unroll
-  for (int o = 16; o; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  const float inv = 1.f / sum;
-  float picked = 0.f, myW = 0.f;
-  int myE = -1;
-  for (int k = 0; k < topk; ++k) {
-    float best = -1.f;
-    int bestIdx = 0x7fffffff;
-#pragma unroll
-    for (int i = 0; i < VPL; ++i) if (v[i] > best) { best = v[i]; bestIdx = i * 32 + lane; }
-#pragma unroll
-    for (int o = 16; o; o >>= 1) {
-      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, bestIdx, o);
-      if (ob > best || (ob == best && oi < bestIdx)) { best = ob; bestIdx = oi; }
-    }
-    if ((bestIdx & 31) == lane) {
-#pragma unroll
-      for (int i = 0; i < VPL; ++i) if (i == (bestIdx >> 5)) v[i] = -1.f;
-    }
-    picked += best * inv;
-    if (lane == k) { myW = best * inv; myE = bestIdx; }
-  }
+  int myE; float myW;
+  purlin::moe::routeToken<VPL>(logits + size_t(warp) * experts, experts, topk, normalize, lane, myE, myW);
   if (lane < topk) {
     topkIdx[size_t(warp) * topk + lane] = myE;
-    topkWeight[size_t(warp) * topk + lane] = normalize ? myW / picked : myW;
+    topkWeight[size_t(warp) * topk + lane] = myW;
     slot[size_t(warp) * topk + lane] = int32_t(atomicAdd(counters + myE, 1u));
   }
 }
@@ -91,7 +62,7 @@ extern "C" int purlin_moe_route_noalloc(const float* logits, int tokens, int exp
     return 1;
   }
   if (topk < 1 || topk > 8 || topk > experts) { purlin::setError("purlin_moe_route_noalloc: top-k must be 1..8"); return 1; }
-  if (tokens < 0 || !logits || !topkIdx || !topkWeight || !slot) { purlin::setError("purlin_moe_route_noalloc: null argument"); return 1; }
+  if (tokens < 0 || tokens > (1 << 26) || !logits || !topkIdx || !topkWeight || !slot) { purlin::setError("purlin_moe_route_noalloc: null argument"); return 1; }
   if (tokens == 0) return 0;
   int device = 0;
   cudaError_t e = cudaGetDevice(&device);

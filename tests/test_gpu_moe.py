@@ -44,3 +44,33 @@ def test_moe_block_world_of_one_matches_fp32_reference():
     y2 = moe(x)            # a second layer call reuses the buffers
     moe.ep.check()
     assert torch.equal(y, y2)
+
+
+def test_route_kernel_is_total_and_matches_the_host_restatement():
+    """Rows of NaN, +inf, -inf and rows with fewer than top-k usable logits: the kernel must return k distinct experts
+    inside [0, experts) with finite weights, equal to the host restatement of the same arithmetic."""
+    sys.path.insert(0, HERE)
+    from test_moe_route_cpu import route_host
+    from purlin_b200.parallel.expert_parallel import ExpertParallelContext
+    dev = torch.device("cuda", 0)
+    tokens, experts, topk = 64, 64, 8
+    ep = ExpertParallelContext(None, dev, max_tokens=tokens, hidden=256, experts=experts, topk=topk)
+    g = torch.Generator(device=dev).manual_seed(2)
+    logits = torch.randn(tokens, experts, generator=g, device=dev)
+    logits[0] = float("nan")
+    logits[1] = float("inf")
+    logits[2] = float("-inf")
+    logits[3] = float("-inf"); logits[3, 5] = 1.0; logits[3, 9] = 2.0
+    logits[4, 7] = float("nan")
+    logits[5, 11] = float("inf")
+    idx, w = ep.route(logits)
+    torch.cuda.synchronize()
+    hi, hw = route_host(logits.cpu().numpy(), topk)
+    assert int(idx.min()) >= 0 and int(idx.max()) < experts
+    assert torch.equal(idx.cpu(), torch.from_numpy(hi))
+    assert torch.isfinite(w).all()
+    assert torch.allclose(w.cpu(), torch.from_numpy(hw), rtol=1e-4, atol=1e-6)
+    x = torch.randn(tokens, 256, generator=g, device=dev).to(torch.bfloat16)
+    ep.dispatch(x)          # ids are in range, so nothing is stored out of bounds
+    ep.check()
+    ep.close()

@@ -167,4 +167,26 @@ def test_table_driven_nvls_and_in_place_plans_pass(world):
                         assert "plan check" not in str(e), f"forced {kw} world {world} bytes {size}: {e}"
     finally:
         tuning.clear()
-    assert built > 300
+    assert built > 250   # in-place reduce-scatter and all-to-all are refused by design
+
+
+def test_forced_tiny_chunks_are_raised_to_fit_the_arrival_counters():
+    """A resident stream may not have more chunks than last-arrival counters (1024): a forced 4 KiB chunk over 16 MiB
+    would give 4096, so the engine raises the chunk size instead."""
+    from purlin_b200 import _native
+    for coll in (P.Collective.ALL_GATHER, P.Collective.ALL_TO_ALL, P.Collective.REDUCE_SCATTER):
+        _, chosen = P.build_plan(coll, 4, 1, 16 << 20)
+        chosen.regime = 1
+        chosen.chunkBytes = 4096
+        plan, _ = P.build_plan(coll, 4, 1, 16 << 20, policy=chosen)
+        for s in plan.active_steps():
+            assert s.chunks <= 1024 or (s.flags & _native.FLAG_CYCLIC and s.slots <= 1024), (int(coll), s.role, s.chunks)
+
+
+@pytest.mark.parametrize("coll", [P.Collective.REDUCE_SCATTER, P.Collective.REDUCE_SCATTER_V, P.Collective.ALL_TO_ALL, P.Collective.ALL_TO_ALL_V])
+def test_in_place_reduce_scatter_and_all_to_all_are_refused(coll):
+    sizes = [1024] * 4 if coll in (P.Collective.REDUCE_SCATTER_V, P.Collective.ALL_TO_ALL_V) else None
+    outs = [1024] * 4 if coll == P.Collective.ALL_TO_ALL_V else None
+    with pytest.raises(RuntimeError, match="in place"):
+        P.build_plan(coll, 4, 2, 0 if sizes else 4096, sizes=sizes, out_sizes=outs, in_place=True)
+    P.build_plan(coll, 4, 2, 0 if sizes else 4096, sizes=sizes, out_sizes=outs, in_place=False)
