@@ -61,10 +61,28 @@ PURLIN_D void tmaLoad2d(uint32_t smemDst, const CUtensorMap* map, int x, int y, 
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(smemDst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// Hint: bring a tile into L2 (no shared-memory destination, nothing to wait for). Issued several k-blocks ahead of the
+// real load it turns a DRAM miss on the critical path into an L2 hit.
+PURLIN_D void tmaPrefetchL2(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 PURLIN_D void tmaPrefetchDescriptor(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 PURLIN_D void fenceProxyAsync() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Tile store: shared memory (this CTA) -> global memory, tracked by the issuing thread's bulk async-groups. Out-of-range
+// parts of the box are clipped. Writers of the shared-memory tile run fenceProxyAsyncShared() before the issuing thread
+// is told (their generic-proxy stores must be visible to the async proxy).
+PURLIN_D void fenceProxyAsyncShared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+PURLIN_D void tmaStore2d(const CUtensorMap* map, int x, int y, uint32_t smemSrc) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(smemSrc), "r"(x), "r"(y) : "memory");
+}
+PURLIN_D void bulkCommitGroup() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// at most N of this thread's groups may still be READING their shared-memory source
+template <int N> PURLIN_D void bulkWaitGroupRead() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+// at most N of this thread's groups may still be in flight at all (their global writes included)
+template <int N> PURLIN_D void bulkWaitGroup() { asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ---- CTA pairs (cluster of two): the pair shares one 256-row MMA; CTA 0 issues it ----
 PURLIN_D uint32_t clusterCtaRank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }

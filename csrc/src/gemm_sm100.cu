@@ -8,7 +8,12 @@
 //
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer   cp.async.bulk.tensor (no cluster multicast) into a ring of 128B-swizzled stages
-//   warp 1      MMA issuer     one thread issues tcgen05.mma (128 x bn x 16) into one of two TMEM accumulators
+//   warp 1      MMA issuer     one thread issues tcgen05.mma (128 x bn x 16) into the TMEM accumulators
+//                              ACCS = 1: tiles alternate between two accumulators (epilogue of tile t under tile t+1)
+//                              ACCS = 2: a tile is two accumulators tall (two blocks of A rows against one block of B):
+//                                        a third fewer operand bytes per flop, and consecutive MMAs alternate between
+//                                        the accumulators while they share the B operand, which the tensor pipe rewards
+//                                        (measured on B200: +13 % over back-to-back MMAs into one accumulator)
 //   warps 2-5   epilogue       tcgen05.ld -> registers -> fused epilogue -> global / peer memory
 //   warps 6-9   communication  (all-gather variant) push this rank's activation rows into every peer's buffer
 //
@@ -54,21 +59,26 @@ constexpr int kThreadsComm = 32 * (2 + kEpiWarps + kCommWarps);
 constexpr int kSmemLimit = 227 * 1024;
 constexpr int kBarrierBytes = 256;
 constexpr int kMaxStages = 8;
-constexpr int kScratchPitch = 272;              // bytes per row of the epilogue's transpose scratch (256 + 16: conflict-free)
-constexpr int kScratchBytes = kEpiWarps * 32 * kScratchPitch;   // reduce-scatter variant only
+// The epilogue's staging tiles: every epilogue warp owns kStageTiles tiles of 32 rows x 64 output columns (bf16, 128-byte rows,
+// 128-byte swizzle), filled from its TMEM lanes and drained row-contiguously: by a TMA store, by coalesced stores into
+// a peer's memory, or by the owner's sum over the peers' partial tiles.
+constexpr int kStageTileBytes = 32 * 128;
+constexpr int kStageTiles = 4;                  // per warp: up to three TMA stores in flight while the fourth tile is filled
+constexpr int kStagingBytes = kEpiWarps * kStageTiles * kStageTileBytes;   // 64 KiB
 
 enum { kEpiStore = 0, kEpiSwiglu = 1 };
 enum { kCommNone = 0, kCommAG = 1, kCommRS = 2 };
 
 struct Params {
-  int M, N, K, bn, stages;
+  int M, N, K, bn, stages;             // bn: columns of a tile (one MMA); a tile is ACCS x CTAS x 128 rows tall
   int tilesM, tilesN;
+  int items, fullItems;                // work items: tiles [0, fullItems) whole, then the remaining tiles as single-accumulator halves
   __nv_bfloat16* C;
   int ldc;
   uint32_t* status;
   uint64_t timeoutNs;
   // tensor parallel
-  int rank, world, blocksPerRank;      // blocksPerRank = rows per rank / 128
+  int rank, world, blocksPerRank;      // blocksPerRank = rows per rank / rows per tile
   uint64_t* epoch;                     // device call counter (flag values and buffer parity derive from it)
   uint32_t* exitCounter;
   // all-gather -> GEMM
@@ -83,11 +93,9 @@ struct Params {
   __nv_bfloat16* partialBuf[kMaxRanks];// every rank's receive buffers: 2 parities x [world slots][M / world, N]
   uint64_t* tileReady[kMaxRanks];      // every rank's flags, [world][blocksPerRank][tilesN][4 row quarters]
   size_t partialParityStride;          // elements between the two parities
-  int epiPipe;                         // 1: the epilogue overlaps the next chunk's TMEM load with the current chunk's arithmetic
-  int rsScratch;                       // 1: remote tiles leave through a shared-memory transpose (long contiguous runs per row)
 };
 
-struct alignas(64) Maps { CUtensorMap a, b, aLocal, a1; };   // a1: gather buffer of odd calls (all-gather variant)
+struct alignas(64) Maps { CUtensorMap a, b, aLocal, a1, c; };   // a1: gather buffer of odd calls (all-gather variant); c: output, 64 x 32 boxes
 
 PURLIN_D void recordTimeout(const Params& p, uint32_t where, uint32_t a, uint32_t b) {
   if (p.status && atomicCAS(p.status, 0u, uint32_t(kStatusTimeoutBarrier)) == 0u) { p.status[1] = where; p.status[2] = a; p.status[3] = b; __threadfence(); }
@@ -111,7 +119,7 @@ PURLIN_D uint32_t packBf16(float lo, float hi) {
 }
 PURLIN_D float bf16lo(uint32_t w) { return __uint_as_float(w << 16); }
 PURLIN_D float bf16hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
-PURLIN_D float silu(float x) { return x / (1.f + __expf(-x)); }
+PURLIN_D float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 
 PURLIN_D void stShared16(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
@@ -120,22 +128,6 @@ PURLIN_D Vec16 ldShared16(uint32_t addr) {
   Vec16 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x[0]), "=r"(v.x[1]), "=r"(v.x[2]), "=r"(v.x[3]) : "r"(addr) : "memory");
   return v;
-}
-
-// 32 fp32 accumulator values of one row -> bf16 -> global (or peer) memory. Two 32-byte stores when the row pitch
-// keeps them aligned (whole sectors, and NVLink-friendly when `out` is peer memory), 16-byte stores otherwise.
-PURLIN_D void storeChunkBf16(__nv_bfloat16* out, const uint32_t (&r)[32], int col, int N, bool wide) {
-  uint32_t o[16];
-#pragma unroll
-  for (int i = 0; i < 16; ++i) o[i] = packBf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
-  if (wide && col + 32 <= N) {
-    st32(out, Vec32{{o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]}});
-    st32(out + 16, Vec32{{o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]}});
-  } else {
-#pragma unroll
-    for (int g = 0; g < 4; ++g)
-      if (col + g * 8 + 8 <= N) st16(out + g * 8, Vec16{{o[4 * g], o[4 * g + 1], o[4 * g + 2], o[4 * g + 3]}});
-  }
 }
 
 // order in which (CTAS x 128)-row blocks are visited
@@ -181,25 +173,73 @@ PURLIN_D void tileCoord(const Params& p, int t, int& mIdx, int& nBlk) {
 }
 
 
-// CTAS = 1: every CTA owns 128 x bn tiles. CTAS = 2: a cluster of two CTAs owns 256 x bn tiles; each CTA loads its
+// The owner's sum over one staging tile: this rank's own partial (bf16, in shared memory) and every peer's partial tile
+// (in this GPU's receive buffer), added in ascending rank order in fp32. A lane handles 16 bytes of a row; an access of
+// the warp covers four rows x 128 contiguous bytes. ROWS row groups (of the 8) are in flight at a time.
+template <int ROWS, int QMAX>
+PURLIN_D void ownerSum(uint32_t buf, const __nv_bfloat16* peer0, size_t slotStride, int ldPartial, __nv_bfloat16* out0, int ldo,
+                       int rank, int world, int rowInGroup, int piece, bool colOk) {
+#pragma unroll 1
+  for (int i = 0; i < 8; i += ROWS) {
+    Vec16 own[ROWS], v[ROWS][QMAX];
+#pragma unroll
+    for (int h = 0; h < ROWS; ++h) {
+      const int rr = 4 * (i + h) + rowInGroup;
+      own[h] = ldShared16(buf + uint32_t(rr) * 128u + (uint32_t(piece ^ (rr & 7)) << 4));
+#pragma unroll
+      for (int q = 0; q < QMAX; ++q)
+        if (q < world && q != rank && colOk) v[h][q] = ld16(peer0 + size_t(q) * slotStride + size_t(rr) * ldPartial);
+    }
+#pragma unroll
+    for (int h = 0; h < ROWS; ++h) {
+      const int rr = 4 * (i + h) + rowInGroup;
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+#pragma unroll
+      for (int q = 0; q < QMAX; ++q) {
+        if (q < world) {
+          const Vec16 w = q == rank ? own[h] : v[h][q];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) { acc[2 * e] += bf16lo(w.x[e]); acc[2 * e + 1] += bf16hi(w.x[e]); }
+        }
+      }
+      if (colOk) st16(out0 + size_t(rr) * ldo, Vec16{{packBf16(acc[0], acc[1]), packBf16(acc[2], acc[3]), packBf16(acc[4], acc[5]), packBf16(acc[6], acc[7])}});
+    }
+  }
+}
+
+// Work item i -> tile and the accumulators (row blocks) of it that the item covers. With two accumulators per tile the
+// tiles of a small last wave are issued as halves (one accumulator each): the tail costs half a wave instead of a whole one.
+template <int ACCS>
+PURLIN_D void itemOf(const Params& p, int i, int& tile, int& first, int& count) {
+  if (ACCS == 1 || i < p.fullItems) { tile = i; first = 0; count = ACCS; }
+  else { const int j = i - p.fullItems; tile = p.fullItems + (j >> 1); first = j & 1; count = 1; }
+}
+
+// CTAS = 1: every CTA owns 128 x bn tiles. CTAS = 2: a cluster of two CTAs owns 256-row tiles; each CTA loads its
 // 128 rows of A and its half of B's columns, CTA 0 issues one 256-row MMA for the pair (cta_group::2), so every
 // byte of B crosses L2 -> shared memory once per 256 rows instead of once per 128.
-template <int EPI, int COMM, int CTAS>
+// ACCS = 2 (pairs only): the tile is 2 x 256 rows tall; each k-block of B meets two blocks of A, one per accumulator.
+template <int EPI, int COMM, int CTAS, int ACCS>
 __global__ void __launch_bounds__(COMM == kCommAG ? kThreadsComm : kThreadsPlain, 1)
 gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) {
   extern __shared__ unsigned char smemRaw[];
   const uint32_t rawAddr = tc::smemAddr(smemRaw);
   const uint32_t base = (rawAddr + 1023u) & ~1023u;          // swizzled tiles need 1024-byte alignment
   unsigned char* smem = smemRaw + (base - rawAddr);
-  const int bnLocal = p.bn / CTAS;                           // B columns this CTA keeps in shared memory
-  const int stageBytes = kABytes + bnLocal * kBK * 2;
-  const uint32_t barBase = base + uint32_t(p.stages) * stageBytes;
+  const int bnLocal = p.bn / CTAS;                           // B columns of one accumulator this CTA keeps in shared memory
+  const int bBytes = bnLocal * kBK * 2;
+  const int stageBytes = ACCS * kABytes + bBytes;            // [A block 0][A block 1][B]
+  const int perRank128 = p.blocksPerRank * ACCS * CTAS;      // 128-row blocks per rank
+  const uint32_t stagingAll = base + uint32_t(p.stages) * stageBytes;     // 1024-byte aligned: stages are multiples of 8 KiB
+  const uint32_t barBase = stagingAll + kStagingBytes;
   // barrier block: full[stages], empty[stages], tmemFull[2], tmemEmpty[2], then the TMEM base word and the abort word
   auto fullBar = [&](int s) { return barBase + 8u * s; };
   auto emptyBar = [&](int s) { return barBase + 8u * (p.stages + s); };
   auto tmemFullBar = [&](int a) { return barBase + 8u * (2 * p.stages + a); };
   auto tmemEmptyBar = [&](int a) { return barBase + 8u * (2 * p.stages + 2 + a); };
-  uint32_t* words = reinterpret_cast<uint32_t*>(smem + size_t(p.stages) * stageBytes + 8 * (2 * p.stages + 4));
+  uint32_t* words = reinterpret_cast<uint32_t*>(smem + size_t(p.stages) * stageBytes + kStagingBytes + 8 * (2 * p.stages + 4));
   volatile uint32_t* tmemBaseWord = words;
   volatile int* abortWord = reinterpret_cast<volatile int*>(words + 1);
 
@@ -230,7 +270,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
   const uint32_t peerBars = CTAS == 2 ? tc::mapToCta(barBase, 1) : barBase;
   (void)peerBars;
 
-  const int numTiles = p.tilesM * p.tilesN;                  // tilesM counts (CTAS x 128)-row blocks
+  const int numItems = p.items;                              // tiles count (CTAS x 128)-row blocks
   const int kBlocks = (p.K + kBK - 1) / kBK;
 
   if (warp == 0) {
@@ -239,44 +279,58 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
       uint32_t st = 0, ph = 0;          // ring position and its phase
       uint64_t seenReady = 0;           // row blocks whose arrival flag this thread has already acquired
       bool ok = true;
-      for (int t = pairIdx; t < numTiles && ok; t += numPairs) {
-        int mIdx, nBlk;
-        tileCoord<COMM>(p, t, mIdx, nBlk);
-        const int mBlk = rowBlockOf<COMM>(p, mIdx) * CTAS + int(ctaRank);      // this CTA's 128-row block
-        const int bRow = nBlk * p.bn + int(ctaRank) * bnLocal;
-        const CUtensorMap* aMap = &maps.a;
-        int aRow = mBlk * kBM;
+      // operand coordinates of a work item: which map A comes from, the first row of this CTA's first A block, B's first row
+      struct Coords { const CUtensorMap* aMap; int aRow, bRow, accCount, mBlk, tile; bool remote; };
+      auto coordsOf = [&](int it) {
+        Coords c;
+        int accFirst, mIdx, nBlk;
+        itemOf<ACCS>(p, it, c.tile, accFirst, c.accCount);
+        tileCoord<COMM>(p, c.tile, mIdx, nBlk);
+        // this CTA's 128-row block of the item's first accumulator; the second accumulator's block is CTAS blocks further
+        c.mBlk = (rowBlockOf<COMM>(p, mIdx) * ACCS + accFirst) * CTAS + int(ctaRank);
+        c.bRow = nBlk * p.bn + int(ctaRank) * bnLocal;
+        c.aMap = &maps.a; c.aRow = c.mBlk * kBM; c.remote = false;
         if constexpr (COMM == kCommAG) {
-          if (parity) aMap = &maps.a1;
-          const int perRank = p.blocksPerRank * CTAS;
-          if (mBlk / perRank == p.rank) {
-            aMap = &maps.aLocal;                       // own rows come straight from the caller's tensor
-            aRow = (mBlk % perRank) * kBM;
-          } else {
-            // rows pushed by a peer: wait for the block's flag, then order those generic-proxy writes
+          if (parity) c.aMap = &maps.a1;
+          if (c.mBlk / perRank128 == p.rank) { c.aMap = &maps.aLocal; c.aRow = (c.mBlk % perRank128) * kBM; }   // own rows: the caller's tensor
+          else c.remote = true;
+        }
+        return c;
+      };
+      for (int it = pairIdx; it < numItems && ok; it += numPairs) {
+        const Coords c = coordsOf(it);
+        if constexpr (COMM == kCommAG) {
+          if (c.remote) {
+            // rows pushed by a peer: wait for each block's flag, then order those generic-proxy writes
             // before this thread's async-proxy reads (TMA)
-            if (mBlk >= 64 || !((seenReady >> mBlk) & 1ull)) {   // a block seen once stays ready for the whole call
-              ok = waitFlag(p.rowReady[p.rank] + mBlk, epoch, abortWord, p.timeoutNs);
-              if (!ok) { recordTimeout(p, 4, mBlk, 0); break; }
-              tc::fenceProxyAsync();
-              if (mBlk < 64) seenReady |= 1ull << mBlk;
+            for (int a = 0; a < c.accCount && ok; ++a) {
+              const int mBlk = c.mBlk + a * CTAS;
+              if (mBlk >= 64 || !((seenReady >> mBlk) & 1ull)) {   // a block seen once stays ready for the whole call
+                ok = waitFlag(p.rowReady[p.rank] + mBlk, epoch, abortWord, p.timeoutNs);
+                if (!ok) { recordTimeout(p, 4, mBlk, 0); break; }
+                tc::fenceProxyAsync();
+                if (mBlk < 64) seenReady |= 1ull << mBlk;
+              }
             }
+            if (!ok) break;
           }
         }
         for (int kb = 0; kb < kBlocks; ++kb) {
           ok = tc::mbarWait(emptyBar(st), ph ^ 1, abortWord, p.timeoutNs);
-          if (!ok) { recordTimeout(p, 1, t, kb); break; }
-          const uint32_t sA = base + st * uint32_t(stageBytes), sB = sA + kABytes;
+          if (!ok) { recordTimeout(p, 1, c.tile, kb); break; }
+          const uint32_t sA = base + st * uint32_t(stageBytes), sB = sA + ACCS * kABytes;
           if constexpr (CTAS == 2) {
             // both CTAs' bytes are credited to CTA 0's barrier; CTA 0 announces the total
             const uint32_t leaderFull = leaderBars + 8u * st;
-            if (ctaRank == 0) tc::mbarExpectTx(fullBar(st), uint32_t(2 * stageBytes));
-            tc::tmaLoad2dPair(sA, aMap, kb * kBK, aRow, leaderFull);
-            tc::tmaLoad2dPair(sB, &maps.b, kb * kBK, bRow, leaderFull);
+            if (ctaRank == 0) tc::mbarExpectTx(fullBar(st), uint32_t(2 * (c.accCount * kABytes + bBytes)));
+#pragma unroll
+            for (int a = 0; a < ACCS; ++a)
+              if (a < c.accCount) tc::tmaLoad2dPair(sA + uint32_t(a * kABytes), c.aMap, kb * kBK, c.aRow + a * CTAS * kBM, leaderFull);
+            tc::tmaLoad2dPair(sB, &maps.b, kb * kBK, c.bRow, leaderFull);
           } else {
             tc::mbarExpectTx(fullBar(st), uint32_t(stageBytes));
-            tc::tmaLoad2d(sA, aMap, kb * kBK, aRow, fullBar(st));
-            tc::tmaLoad2d(sB, &maps.b, kb * kBK, bRow, fullBar(st));
+            tc::tmaLoad2d(sA, c.aMap, kb * kBK, c.aRow, fullBar(st));
+            tc::tmaLoad2d(sB, &maps.b, kb * kBK, c.bRow, fullBar(st));
           }
           if (++st == uint32_t(p.stages)) { st = 0; ph ^= 1; }
         }
@@ -287,17 +341,31 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
     if (lane == 0 && ctaRank == 0) {
       const uint32_t idesc = tc::instrDescBf16(uint32_t(p.bn), uint32_t(kBM * CTAS));
       // descriptors differ only in their 14-bit start address: keep the constant halves out of the loop
-      const uint64_t descA0 = tc::smemDescSw128(base), descB0 = tc::smemDescSw128(base + kABytes);
-      const uint32_t stageStep = uint32_t(stageBytes) >> 4;
-      uint32_t st = 0, ph = 0, accIt = 0;
+      const uint64_t descA0 = tc::smemDescSw128(base), descB0 = tc::smemDescSw128(base + ACCS * kABytes);
+      const uint32_t stageStep = uint32_t(stageBytes) >> 4, accStep = uint32_t(kABytes) >> 4;
+      uint32_t st = 0, ph = 0;
+      uint32_t accIt = 0;
+      uint32_t use0 = 0, use1 = 0;          // how often each accumulator slot has been used: barrier phase = uses & 1
       bool ok = true;
-      for (int t = pairIdx; t < numTiles && ok; t += numPairs, ++accIt) {
-        const int a = accIt & 1;
-        const uint32_t aph = (accIt >> 1) & 1;
-        ok = tc::mbarWait(tmemEmptyBar(a), aph ^ 1, abortWord, p.timeoutNs);   // epilogues drained this accumulator
+      auto releaseStage = [&](uint32_t stg) {   // the stage is free (in both CTAs) once the MMAs issued so far have read it
+        if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (p.stages + stg)); tc::mmaCommitPair(peerBars + 8u * (p.stages + stg)); }
+        else tc::mmaCommit(emptyBar(stg));
+      };
+      auto accumulatorDone = [&](int a) {      // the accumulator is complete once every MMA issued so far is done
+        if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (2 * p.stages + a)); tc::mmaCommitPair(peerBars + 8u * (2 * p.stages + a)); }
+        else tc::mmaCommit(tmemFullBar(a));
+      };
+      for (int it = pairIdx; it < numItems && ok; it += numPairs, ++accIt) {
+        int t, accFirst, accCount;
+        itemOf<ACCS>(p, it, t, accFirst, accCount);
+        // ACCS = 1: tiles alternate between the slots. ACCS = 2: slot 0 and slot 1 of one tile (a half tile uses slot 0).
+        const int a0 = ACCS == 1 ? int(accIt & 1) : 0;
+        const bool two = ACCS == 2 && accCount == 2;
+        // the epilogues must have drained the accumulators this item writes
+        ok = tc::mbarWait(tmemEmptyBar(a0), ((a0 ? use1 : use0) & 1) ^ 1, abortWord, p.timeoutNs);
+        if (ok && two) ok = tc::mbarWait(tmemEmptyBar(1), (use1 & 1) ^ 1, abortWord, p.timeoutNs);
         if (!ok) { recordTimeout(p, 2, t, 0); break; }
-        tc::fenceAfterThreadSync();
-        const uint32_t tmemD = tmemBase + uint32_t(a) * kAccStride;
+        const uint32_t d0 = tmemBase + uint32_t(a0) * kAccStride, d1 = tmemBase + kAccStride;
         for (int kb = 0; kb < kBlocks; ++kb) {
           ok = tc::mbarWait(fullBar(st), ph, abortWord, p.timeoutNs);
           if (!ok) { recordTimeout(p, 3, t, kb); break; }
@@ -305,195 +373,175 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           const uint64_t da = descA0 + uint64_t(st * stageStep), db = descB0 + uint64_t(st * stageStep);
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            if constexpr (CTAS == 2) tc::mmaPair(tmemD, da + 2 * k, db + 2 * k, idesc, uint32_t((kb | k) != 0));
-            else tc::mma(tmemD, da + 2 * k, db + 2 * k, idesc, uint32_t((kb | k) != 0));
+            const uint32_t accumulate = uint32_t((kb | k) != 0);
+            if constexpr (CTAS == 2) {
+              tc::mmaPair(d0, da + 2 * k, db + 2 * k, idesc, accumulate);
+              // the second accumulator: the other block of A rows against the same slice of B
+              if constexpr (ACCS == 2) { if (two) tc::mmaPair(d1, da + accStep + 2 * k, db + 2 * k, idesc, accumulate); }
+            } else {
+              tc::mma(d0, da + 2 * k, db + 2 * k, idesc, accumulate);
+            }
           }
-          // the stage is free (in both CTAs) once these MMAs have read it
-          if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (p.stages + st)); tc::mmaCommitPair(peerBars + 8u * (p.stages + st)); }
-          else tc::mmaCommit(emptyBar(st));
+          releaseStage(st);
           if (++st == uint32_t(p.stages)) { st = 0; ph ^= 1; }
         }
-        if (ok) {   // the accumulator is complete once every MMA of the tile is done
-          if constexpr (CTAS == 2) { tc::mmaCommitPair(leaderBars + 8u * (2 * p.stages + a)); tc::mmaCommitPair(peerBars + 8u * (2 * p.stages + a)); }
-          else tc::mmaCommit(tmemFullBar(a));
+        if (ok) {
+          accumulatorDone(a0);
+          if (a0) ++use1; else ++use0;
+          if (two) { accumulatorDone(1); ++use1; }
         }
       }
     }
   } else if (warp < 2 + kEpiWarps) {
     // ------------------------------- epilogue -------------------------------
     const int quarter = warp & 3;                // a warp may only touch TMEM lanes [32 * (warp % 4), +32)
-    const int perRank = p.blocksPerRank * CTAS;  // 128-row blocks per rank
     uint32_t accIt = 0;
+    uint32_t use0 = 0, use1 = 0;
+    uint32_t tileCount = 0;                      // staging tiles this warp has filled: they rotate through its buffers
     bool ok = true;
-    for (int t = pairIdx; t < numTiles && ok; t += numPairs, ++accIt) {
-      const int a = accIt & 1;
-      const uint32_t aph = (accIt >> 1) & 1;
-      int mIdx, nBlk;
+    for (int it = pairIdx; it < numItems && ok; it += numPairs, ++accIt) {
+      int t, accFirst, accCount, mIdx, nBlk;
+      itemOf<ACCS>(p, it, t, accFirst, accCount);
       tileCoord<COMM>(p, t, mIdx, nBlk);
-      const int mBlk = rowBlockOf<COMM>(p, mIdx) * CTAS + int(ctaRank);
+      const int rowBlk = rowBlockOf<COMM>(p, mIdx);
       const int n0 = nBlk * p.bn;
-      ok = tc::mbarWait(tmemFullBar(a), aph, abortWord, p.timeoutNs);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) { if (lane == 0) recordTimeout(p, 5, t, 0); break; }
-      tc::fenceAfterThreadSync();
-      const uint32_t taddr = tmemBase + (uint32_t(quarter * 32) << 16) + uint32_t(a) * kAccStride;
+
+#pragma unroll 1
+      for (int ai = 0; ai < accCount && ok; ++ai) {
+      const int a = ACCS == 1 ? int(accIt & 1) : ai;      // accumulator slot
+      const int mBlk = (rowBlk * ACCS + accFirst + ai) * CTAS + int(ctaRank);   // this CTA's 128-row block of the accumulator
       const int rowInTile = quarter * 32 + lane;
       const int row = mBlk * kBM + rowInTile;
-
       int dstRank = p.rank, rowInShard = row;
       const __nv_bfloat16* partialBase = nullptr;   // slot 0 of this row inside the receive buffer
       size_t slotStride = 0;
       bool reduceOwn = false;
       if constexpr (COMM == kCommRS) {
-        dstRank = mBlk / perRank;
-        rowInShard = row - dstRank * perRank * kBM;
+        dstRank = mBlk / perRank128;
+        rowInShard = row - dstRank * perRank128 * kBM;
         reduceOwn = dstRank == p.rank && p.world > 1;
         if (reduceOwn) {
-          // every peer's partial tile (this row quarter) must have landed
+          slotStride = size_t(perRank128) * kBM * p.N;
+          partialBase = p.partialBuf[p.rank] + size_t(parity) * p.partialParityStride + size_t(rowInShard) * p.N;
+          // every peer's partial of this tile (this row quarter) must have landed
           int good = 1;
           if (lane < p.world && lane != p.rank) {
-            const uint64_t* f = p.tileReady[p.rank] + ((size_t(lane) * perRank + (mBlk % perRank)) * p.tilesN + nBlk) * 4 + quarter;
+            const uint64_t* f = p.tileReady[p.rank] + ((size_t(lane) * perRank128 + (mBlk % perRank128)) * p.tilesN + nBlk) * 4 + quarter;
             good = waitFlag(f, epoch, abortWord, p.timeoutNs) ? 1 : 0;
           }
           ok = __all_sync(0xffffffffu, good);
-          if (!ok) { if (lane == 0) recordTimeout(p, 6, t, 0); break; }
-          slotStride = size_t(perRank) * kBM * p.N;
-          partialBase = p.partialBuf[p.rank] + size_t(parity) * p.partialParityStride + size_t(rowInShard) * p.N;
+          if (!ok) { if (lane == 0) recordTimeout(p, 6, t, ai); break; }
         }
       }
+      ok = tc::mbarWait(tmemFullBar(a), (a ? use1 : use0) & 1, abortWord, p.timeoutNs);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { if (lane == 0) recordTimeout(p, 5, t, ai); break; }
+      if (a) ++use1; else ++use0;
+      tc::fenceAfterThreadSync();
+      const uint32_t taddr = tmemBase + (uint32_t(quarter * 32) << 16) + uint32_t(a) * kAccStride;
 
-      bool viaScratch = false;
-      if constexpr (COMM == kCommRS && EPI == kEpiStore) {
-        viaScratch = p.rsScratch && dstRank != p.rank && p.bn % 128 == 0 && n0 + p.bn <= p.N;
-        if (viaScratch) {
-          // Rows of a remote tile leave as 128-byte runs: the 32 lanes hold 32 different rows (64 bytes each per TMEM
-          // load), so a direct store would put 32 separate 32-byte sectors on NVLink per instruction. Through the
-          // scratch each store instruction writes 4 rows x 128 contiguous bytes.
-          const uint32_t scratch = barBase + kBarrierBytes + uint32_t(warp - 2) * 32u * kScratchPitch;
-          __nv_bfloat16* tileOut = p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride +
-                                   (size_t(p.rank) * perRank * kBM + size_t(rowInShard - lane)) * p.N + n0;   // row of lane 0
-          for (int h0 = 0; h0 < p.bn; h0 += 128) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              uint32_t r[32];
-              tc::tmemLoad32(taddr + uint32_t(h0 + c * 32), r);
-              tc::tmemLoadWait();
-              const uint32_t rowAddr = scratch + uint32_t(lane) * kScratchPitch + uint32_t(c) * 64u;
-#pragma unroll
-              for (int g = 0; g < 4; ++g)
-                stShared16(rowAddr + g * 16, packBf16(__uint_as_float(r[8 * g]), __uint_as_float(r[8 * g + 1])), packBf16(__uint_as_float(r[8 * g + 2]), __uint_as_float(r[8 * g + 3])),
-                           packBf16(__uint_as_float(r[8 * g + 4]), __uint_as_float(r[8 * g + 5])), packBf16(__uint_as_float(r[8 * g + 6]), __uint_as_float(r[8 * g + 7])));
-            }
-            __syncwarp();
-            const int rowInGroup = lane >> 3, piece = lane & 7;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = 4 * i + rowInGroup;
-              const uint32_t src = scratch + uint32_t(rr) * kScratchPitch + uint32_t(piece) * 16u;
-              const Vec16 lo = ldShared16(src), hi = ldShared16(src + 128);
-              __nv_bfloat16* o = tileOut + size_t(rr) * p.N + h0;
-              st16(o + piece * 8, lo);
-              st16(o + 64 + piece * 8, hi);
-            }
-            __syncwarp();
-          }
-        }
-      }
-      // One 32-column chunk of this warp's rows: convert (and activate) the accumulators and store them.
-      auto emitChunk = [&](const uint32_t (&r)[32], int c0) {
-        const int col = n0 + c0;
+      // Where this warp's 32 rows go: `outRow0` is the row of lane 0 at output column 0, `ldo` its pitch in elements.
+      constexpr int kOut = EPI == kEpiSwiglu ? 16 : 32;     // output columns per 32 accumulator columns
+      constexpr int kPerTile = 64 / kOut;                    // TMEM chunks per staging tile
+      const int outBound = EPI == kEpiSwiglu ? p.N / 2 : p.N;
+      const int outCol0 = EPI == kEpiSwiglu ? n0 / 2 : n0;
+      const int perRank = perRank128;
+      const int row0 = row - lane;
+      const bool remote = COMM == kCommRS && dstRank != p.rank;
+      const int ldo = COMM == kCommRS ? (remote ? p.N : p.ldc) : p.ldc;
+      __nv_bfloat16* outRow0;
+      if (remote) outRow0 = p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride + (size_t(p.rank) * perRank * kBM + size_t(rowInShard - lane)) * p.N;
+      else if (COMM == kCommRS) outRow0 = p.C + size_t(rowInShard - lane) * p.ldc;
+      else outRow0 = p.C + size_t(row0) * p.ldc;
+      const int rowsValid = COMM == kCommRS ? 32 : (p.M - row0 < 32 ? p.M - row0 : 32);    // rows of this warp inside the output
+      const int nChunks = p.bn / 32;
+
+      // 32 accumulator columns of this lane's row -> bf16 (activated) -> chunk `slot` of the staging tile
+      const uint32_t stagingWarp = stagingAll + uint32_t(warp - 2) * uint32_t(kStageTiles * kStageTileBytes);
+      auto stageChunk = [&](const uint32_t (&r)[32], uint32_t buf, int slot) {
+        uint32_t o[kOut / 2];
         if constexpr (EPI == kEpiSwiglu) {
-          // columns [c0, c0+16) are gate, [c0+16, c0+32) are up, both for output columns (n0 + c0) / 2 + [0, 16)
-          if (row < p.M) {
-            uint32_t o[8];
+          // columns [0, 16) are gate, [16, 32) are up, both for the same 16 output columns
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
-              const float u0 = __uint_as_float(r[16 + 2 * i]), u1 = __uint_as_float(r[16 + 2 * i + 1]);
-              o[i] = packBf16(silu(g0) * u0, silu(g1) * u1);
-            }
-            __nv_bfloat16* out = p.C + size_t(row) * p.ldc + col / 2;
-            if (col / 2 + 16 <= p.ldc) {
-              if ((reinterpret_cast<uintptr_t>(out) & 31u) == 0) st32(out, Vec32{{o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]}});
-              else { st16(out, Vec16{{o[0], o[1], o[2], o[3]}}); st16(out + 8, Vec16{{o[4], o[5], o[6], o[7]}}); }
-            }
-          }
-        } else if constexpr (COMM == kCommRS) {
-          if (reduceOwn) {
-            // ascending rank order; own accumulator takes this rank's place in the sum. All peers' copies of the
-            // 32 columns are requested before any is consumed (up to 8 peers x 64 bytes in flight per thread).
-            float acc[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) acc[e] = 0.f;
-            const bool full = col + 32 <= p.N;
-            for (int q0 = 0; q0 < p.world; q0 += 8) {
-              Vec16 v[8][4];
-#pragma unroll
-              for (int b = 0; b < 8; ++b)
-                if (q0 + b < p.world && q0 + b != p.rank) {
-                  const __nv_bfloat16* src = partialBase + size_t(q0 + b) * slotStride + col;
-#pragma unroll
-                  for (int g = 0; g < 4; ++g)
-                    if (full || col + g * 8 + 8 <= p.N) v[b][g] = ld16(src + g * 8);
-                }
-#pragma unroll
-              for (int b = 0; b < 8; ++b) {
-                if (q0 + b >= p.world) break;
-                if (q0 + b == p.rank) {
-#pragma unroll
-                  for (int e = 0; e < 32; ++e) acc[e] += __uint_as_float(r[e]);
-                } else {
-#pragma unroll
-                  for (int g = 0; g < 4; ++g)
-                    if (full || col + g * 8 + 8 <= p.N) {
-#pragma unroll
-                      for (int e = 0; e < 4; ++e) { acc[g * 8 + 2 * e] += bf16lo(v[b][g].x[e]); acc[g * 8 + 2 * e + 1] += bf16hi(v[b][g].x[e]); }
-                    }
-                }
-              }
-            }
-            uint32_t accBits[32];
-#pragma unroll
-            for (int e = 0; e < 32; ++e) accBits[e] = __float_as_uint(acc[e]);
-            __nv_bfloat16* out = p.C + size_t(rowInShard) * p.ldc + col;
-            storeChunkBf16(out, accBits, col, p.N, (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
-          } else {
-            __nv_bfloat16* out = (dstRank == p.rank)
-                ? p.C + size_t(rowInShard) * p.ldc + col      // world of one: plain store
-                : p.partialBuf[dstRank] + size_t(parity) * p.partialParityStride + (size_t(p.rank) * perRank * kBM + rowInShard) * p.N + col;
-            storeChunkBf16(out, r, col, p.N, (p.N % 16) == 0 && (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
+          for (int i = 0; i < 8; ++i) {
+            const float g0 = __uint_as_float(r[2 * i]), g1 = __uint_as_float(r[2 * i + 1]);
+            const float u0 = __uint_as_float(r[16 + 2 * i]), u1 = __uint_as_float(r[16 + 2 * i + 1]);
+            o[i] = packBf16(silu(g0) * u0, silu(g1) * u1);
           }
         } else {
-          if (row < p.M) {
-            __nv_bfloat16* out = p.C + size_t(row) * p.ldc + col;
-            storeChunkBf16(out, r, col, p.N, (reinterpret_cast<uintptr_t>(out) & 31u) == 0);
-          }
+#pragma unroll
+          for (int i = 0; i < 16; ++i) o[i] = packBf16(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1]));
+        }
+        const uint32_t rowAddr = buf + uint32_t(lane) * 128u;
+#pragma unroll
+        for (int j = 0; j < kOut / 8; ++j) {
+          const int chunk = slot * (kOut / 8) + j;
+          stShared16(rowAddr + (uint32_t(chunk ^ (lane & 7)) << 4), o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
       };
-      if (!viaScratch) {
-        if (p.epiPipe && COMM != kCommRS) {
-          // software-pipelined: the next chunk's TMEM load is in flight while this chunk is converted and stored
-          uint32_t ra[32], rb[32];
-          tc::tmemLoad32(taddr, ra);
-          for (int c0 = 0; c0 < p.bn; c0 += 64) {
-            tc::tmemLoadWaitFor(ra);
-            const bool second = c0 + 32 < p.bn;
-            if (second) tc::tmemLoad32(taddr + uint32_t(c0 + 32), rb);
-            emitChunk(ra, c0);
-            if (second) {
+
+      // Software pipeline over the accumulator: the TMEM load of the next 32 columns is in flight while the current ones
+      // are converted and staged; every kPerTile chunks a staging tile is full and is drained.
+      uint32_t ra[32], rb[32];
+      tc::tmemLoad32(taddr, ra);
+#pragma unroll 1
+      for (int c0 = 0; c0 < nChunks; c0 += kPerTile) {
+        const uint32_t buf = stagingWarp + (tileCount % uint32_t(kStageTiles)) * kStageTileBytes;
+        ++tileCount;
+        // the TMA store that last read this tile (kStageTiles tiles ago) must be done reading it
+        if (lane == 0) tc::bulkWaitGroupRead<kStageTiles - 1>();
+        __syncwarp();
+        int filled = 0;
+#pragma unroll
+        for (int sl = 0; sl < kPerTile; ++sl) {
+          const int c = c0 + sl;
+          if (c < nChunks) {
+            if (sl % 2 == 0) {
+              tc::tmemLoadWaitFor(ra);
+              if (c + 1 < nChunks) tc::tmemLoad32(taddr + uint32_t((c + 1) * 32), rb);
+              stageChunk(ra, buf, sl);
+            } else {
               tc::tmemLoadWaitFor(rb);
-              if (c0 + 64 < p.bn) tc::tmemLoad32(taddr + uint32_t(c0 + 64), ra);
-              emitChunk(rb, c0 + 32);
+              if (c + 1 < nChunks) tc::tmemLoad32(taddr + uint32_t((c + 1) * 32), ra);
+              stageChunk(rb, buf, sl);
             }
-          }
-        } else {
-          for (int c0 = 0; c0 < p.bn; c0 += 32) {
-            uint32_t r[32];
-            tc::tmemLoad32(taddr + uint32_t(c0), r);
-            tc::tmemLoadWait();
-            emitChunk(r, c0);
+            filled = sl + 1;
           }
         }
+        // ---- drain the tile: output columns [oc, oc + cols) of the warp's 32 rows ----
+        const int oc = outCol0 + (c0 / kPerTile) * 64, cols = filled * kOut;
+        if (oc >= outBound || rowsValid <= 0) continue;
+        if constexpr (COMM != kCommRS) {
+          // a whole tile (or one whose unused columns fall outside the matrix, where the store is clipped) leaves by TMA
+          if (cols == 64 || oc + cols >= outBound) {
+            tc::fenceProxyAsyncShared();
+            __syncwarp();
+            if (lane == 0) { tc::tmaStore2d(&maps.c, oc, row0, buf); tc::bulkCommitGroup(); }
+            continue;
+          }
+        }
+        __syncwarp();
+        const int rowInGroup = lane >> 3, piece = lane & 7;
+        const bool colOk = piece * 8 < cols && oc + piece * 8 + 8 <= outBound;
+        if (COMM == kCommRS && reduceOwn) {
+          const __nv_bfloat16* peer0 = partialBase - size_t(lane) * p.N + oc + piece * 8;     // row of lane 0, slot 0, this lane's columns
+          __nv_bfloat16* out0 = outRow0 + oc + piece * 8;
+          if (p.world <= 8) ownerSum<2, 8>(buf, peer0, slotStride, p.N, out0, ldo, p.rank, p.world, rowInGroup, piece, colOk);
+          else ownerSum<1, kMaxRanks>(buf, peer0, slotStride, p.N, out0, ldo, p.rank, p.world, rowInGroup, piece, colOk);
+        } else {
+          Vec16 v[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + rowInGroup;
+            v[i] = ldShared16(buf + uint32_t(rr) * 128u + (uint32_t(piece ^ (rr & 7)) << 4));
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int rr = 4 * i + rowInGroup;
+            if (colOk && rr < rowsValid) st16(outRow0 + size_t(rr) * ldo + oc + piece * 8, v[i]);
+          }
+        }
+        __syncwarp();
       }
       // hand the accumulator back to the MMA warp (of CTA 0)
       tc::fenceBeforeThreadSync();
@@ -504,7 +552,7 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
       }
       if constexpr (COMM == kCommRS) {
         if (dstRank != p.rank) {
-          // this warp's 32 rows of the tile are in the peer's memory: publish them
+          // this warp's 32 rows of these columns are in the peer's memory: publish them
           __syncwarp();
           if (lane == 0) {
             uint64_t* f = p.tileReady[dstRank] + ((size_t(p.rank) * perRank + (mBlk % perRank)) * p.tilesN + nBlk) * 4 + quarter;
@@ -512,13 +560,15 @@ gemmKernel(const __grid_constant__ Maps maps, const __grid_constant__ Params p) 
           }
         }
       }
+      }   // accumulators of the item
     }
+    if (lane == 0) tc::bulkWaitGroup<0>();       // every TMA store of this warp has reached global memory
   } else {
     // ------------------------------- communication warps (all-gather push) -------------------------------
     if constexpr (COMM == kCommAG) {
       const int ct = threadIdx.x - 32 * (2 + kEpiWarps), cn = 32 * p.commWarps;   // p.commWarps of the 4 warps push
       if (ct < cn) {
-      const int perRank = p.blocksPerRank * CTAS;
+      const int perRank = perRank128;
       const size_t blockBytes = size_t(kBM) * p.K * 2;
       const int items = (p.world - 1) * perRank * p.pushParts;
       for (int item = blockIdx.x; item < items; item += gridDim.x) {
@@ -578,7 +628,8 @@ EncodeFn encodeFn() {
   return fn;
 }
 
-// [rows, cols] bf16 row-major; box = boxRows x 64 columns, 128-byte swizzle
+// [rows, cols] bf16 row-major; box = boxRows x 64 columns (128 bytes), 128-byte swizzle. Operands are loaded through
+// such maps (128 or fewer rows per box), the output is stored through one with 32-row boxes (one epilogue warp's rows).
 bool makeMap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, uint32_t boxRows) {
   EncodeFn fn = encodeFn();
   if (!fn) { setError("cuTensorMapEncodeTiled is not available from this driver"); return false; }
@@ -597,6 +648,26 @@ bool makeMap(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t cols, ui
 int smCount() {
   static int n = [] { int d = 0, v = 148; cudaGetDevice(&d); cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, d); return v; }();
   return n;
+}
+
+// Environment switches, read once per process (they select code paths for experiments, not per-call behaviour).
+struct Switches {
+  bool singleCta, oneAcc;
+  int agCommWarps, agPushParts;
+};
+const Switches& switches() {
+  static const Switches sw = [] {
+    Switches v{};
+    auto num = [](const char* name, int dflt) { const char* e = std::getenv(name); return e ? std::atoi(e) : dflt; };
+    v.singleCta = std::getenv("PURLIN_GEMM_SINGLE_CTA") != nullptr;
+    v.oneAcc = std::getenv("PURLIN_GEMM_ONE_ACC") != nullptr;
+    // Few pushing warps per CTA pace the remote stores: a saturated NVLink store queue stalls every memory
+    // instruction of its SM, the epilogue's included.
+    v.agCommWarps = std::min(std::max(num("PURLIN_AG_COMM_WARPS", 1), 1), kCommWarps);
+    v.agPushParts = std::min(std::max(num("PURLIN_AG_PUSH_PARTS", 8), 1), 64);
+    return v;
+  }();
+  return sw;
 }
 
 // tile width: fewest idle SMs in the last wave, then the widest tile
@@ -618,30 +689,38 @@ int chooseBn(int M, int N, int epilogue) {
 
 // a CTA pair per 256-row block when the rows allow it (and PURLIN_GEMM_SINGLE_CTA is not set)
 int ctasFor(int M, int rowsPerRank) {
-  static const bool single = std::getenv("PURLIN_GEMM_SINGLE_CTA") != nullptr;
-  if (single) return 1;
+  if (switches().singleCta) return 1;
   return (rowsPerRank % (2 * kBM) == 0 && M >= 2 * kBM) ? 2 : 1;
 }
 
-bool fillShape(Params& p, int M, int N, int K, int epilogue, int bn, int ctas, int scratchBytes = 0) {
+struct Shape { int ctas, accs; };
+
+bool fillShape(Params& p, Shape& sh, int M, int N, int K, int epilogue, int bn, int rowsPerRank) {
   if (M <= 0 || N <= 0 || K <= 0) { setError("GEMM dimensions must be positive"); return false; }
   if (K % 8 || N % 8) { setError("N and K must be multiples of 8"); return false; }
+  const int ctas = ctasFor(M, rowsPerRank);
   if (bn == 0) bn = chooseBn(M, N, epilogue);
-  if (bn % 16 || bn < 16 || bn > kMaxBN || (epilogue == kEpiSwiglu && bn % 32)) { setError("tile width must be a multiple of 16 (32 for SwiGLU) up to 256"); return false; }
+  if (bn % 32 || bn < 32 || bn > kMaxBN) { setError("tile width must be a multiple of 32 up to 256"); return false; }
   p.M = M; p.N = N; p.K = K; p.bn = bn;
-  static const bool epiPipe = [] { const char* e = std::getenv("PURLIN_GEMM_EPI_PIPE"); return !e || e[0] != '0'; }();
-  p.epiPipe = epiPipe ? 1 : 0;
   if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
-  p.tilesM = (M + kBM * ctas - 1) / (kBM * ctas); p.tilesN = (N + bn - 1) / bn;
-  const int stageBytes = kABytes + (bn / ctas) * kBK * 2;
-  p.stages = std::min((kSmemLimit - kBarrierBytes - 1024 - scratchBytes) / stageBytes, kMaxStages);
+  // two accumulators per tile (512 rows) whenever the rows allow it: a third fewer operand bytes per flop, and MMAs
+  // that alternate between two accumulators while sharing B run faster than a chain into one accumulator
+  const int accs = (ctas == 2 && !switches().oneAcc && 2 * bn <= kTmemCols && rowsPerRank % (4 * kBM) == 0 && M % (4 * kBM) == 0) ? 2 : 1;
+  sh.ctas = ctas; sh.accs = accs;
+  const int tileRows = kBM * ctas * accs;
+  p.tilesM = (M + tileRows - 1) / tileRows; p.tilesN = (N + bn - 1) / bn;
+  const int stageBytes = accs * kABytes + (bn / ctas) * kBK * 2;
+  p.stages = std::min((kSmemLimit - kBarrierBytes - 1024 - kStagingBytes) / stageBytes, kMaxStages);
+  if (p.stages < 2) { setError("GEMM tile does not leave room for two pipeline stages"); return false; }
   return true;
 }
-size_t smemFor(const Params& p, int ctas) { return size_t(p.stages) * (kABytes + (p.bn / ctas) * kBK * 2) + kBarrierBytes + 1024 + (p.rsScratch ? kScratchBytes : 0); }
+size_t smemFor(const Params& p, const Shape& sh) {
+  return size_t(p.stages) * (sh.accs * kABytes + (p.bn / sh.ctas) * kBK * 2) + kStagingBytes + kBarrierBytes + 1024;
+}
 
-template <int EPI, int COMM, int CTAS>
-int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
-  auto kernel = gemmKernel<EPI, COMM, CTAS>;
+template <int EPI, int COMM, int CTAS, int ACCS>
+int launchImpl(const Maps& maps, const Params& p, const Shape& sh, cudaStream_t stream) {
+  auto kernel = gemmKernel<EPI, COMM, CTAS, ACCS>;
   constexpr int threads = COMM == kCommAG ? kThreadsComm : kThreadsPlain;
   // shared-memory opt-in and cluster occupancy belong to the device's copy of the kernel: resolve them once per device
   static int perDevice[64];
@@ -663,20 +742,54 @@ int launchImpl(const Maps& maps, const Params& p, cudaStream_t stream) {
       if (cudaOccupancyMaxActiveClusters(&n, kernel, &q) == cudaSuccess && n > 0) maxClusters = std::min(maxClusters, n);
     }
   }
-  const int pairs = std::min(p.tilesM * p.tilesN, maxClusters);
+  const int tiles = p.tilesM * p.tilesN;
+  const int pairs = std::min(tiles, maxClusters);
+  Params q = p;
+  q.items = q.fullItems = tiles;
+  if (ACCS == 2) {
+    // a last wave that fills at most half of the CTA pairs is issued as half tiles: half a wave instead of a whole one
+    const int rest = tiles % pairs;
+    if (tiles > pairs && rest > 0 && 2 * rest <= pairs) { q.fullItems = tiles - rest; q.items = q.fullItems + 2 * rest; }
+  }
   cudaLaunchConfig_t cfg{};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension; attr[0].val.clusterDim.x = CTAS; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(pairs * CTAS); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smemFor(p, CTAS); cfg.stream = stream;
+  cfg.gridDim = dim3(pairs * CTAS); cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = smemFor(p, sh); cfg.stream = stream;
   cfg.attrs = attr; cfg.numAttrs = 1;
-  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps, p);
+  const cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, maps, q);
   if (e != cudaSuccess) { setError(std::string("GEMM launch: ") + cudaGetErrorString(e)); return 1; }
   return 0;
 }
 template <int EPI, int COMM>
-int launch(const Maps& maps, const Params& p, int ctas, cudaStream_t stream) {
-  return ctas == 2 ? launchImpl<EPI, COMM, 2>(maps, p, stream) : launchImpl<EPI, COMM, 1>(maps, p, stream);
+int launch(const Maps& maps, const Params& p, const Shape& sh, cudaStream_t stream) {
+  if (sh.ctas == 2) return sh.accs == 2 ? launchImpl<EPI, COMM, 2, 2>(maps, p, sh, stream) : launchImpl<EPI, COMM, 2, 1>(maps, p, sh, stream);
+  return launchImpl<EPI, COMM, 1, 1>(maps, p, sh, stream);
 }
+
+// Tensor maps are pure functions of (pointer, rows, columns, box rows): encoding one costs about a microsecond of host
+// time, and a fused call needs up to four, so each entry point keeps the maps of its last few operand sets.
+struct MapKey {
+  const void* ptr; uint64_t rows, cols; uint32_t box;
+  bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && box == o.box; }
+};
+class MapCache {
+ public:
+  const CUtensorMap* get(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box) {
+    const MapKey k{ptr, rows, cols, box};
+    for (int i = 0; i < kSlots; ++i) if (valid_[i] && keys_[i] == k) return &maps_[i];
+    const int i = next_; next_ = (next_ + 1) % kSlots;
+    valid_[i] = false;
+    if (!makeMap(&maps_[i], ptr, rows, cols, box)) return nullptr;
+    keys_[i] = k; valid_[i] = true;
+    return &maps_[i];
+  }
+ private:
+  static constexpr int kSlots = 16;
+  alignas(64) CUtensorMap maps_[kSlots];
+  MapKey keys_[kSlots] = {};
+  bool valid_[kSlots] = {};
+  int next_ = 0;
+};
 
 }  // namespace
 
@@ -687,6 +800,7 @@ struct PurlinTpContext {
   size_t partialParityStride = 0;
   void* local = nullptr;     // epoch words, exit counters, status, push counters
   uint64_t timeoutNs = 0;
+  MapCache maps;             // tensor maps of recent operand sets (the same tensors come back every step)
 };
 
 namespace {
@@ -714,19 +828,22 @@ extern "C" {
 int purlin_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int epilogue, int bn, uint32_t* status, void* stream) {
   NvtxRange range(epilogue == kEpiSwiglu ? "gemmSwiglu" : "gemm", size_t(M) * size_t(N) * 2);
   Params p{};
-  const int ctas = ctasFor(M, M);
-  if (!fillShape(p, M, N, K, epilogue, bn, ctas)) return 1;
+  Shape sh{};
+  if (!fillShape(p, sh, M, N, K, epilogue, bn, M)) return 1;
+  static thread_local MapCache cache;
+  const CUtensorMap* ma = cache.get(A, uint64_t(M), uint64_t(K), kBM);
+  const CUtensorMap* mb = ma ? cache.get(B, uint64_t(N), uint64_t(K), uint32_t(p.bn / sh.ctas)) : nullptr;
+  const CUtensorMap* mc = mb ? cache.get(C, uint64_t(M), uint64_t(epilogue == kEpiSwiglu ? N / 2 : N), 32) : nullptr;
+  if (!ma || !mb || !mc) return 1;
   Maps maps{};
-  if (!makeMap(&maps.a, A, uint64_t(M), uint64_t(K), kBM)) return 1;
-  if (!makeMap(&maps.b, B, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
-  maps.aLocal = maps.a;
+  maps.a = *ma; maps.b = *mb; maps.aLocal = maps.a; maps.c = *mc;
   p.C = static_cast<__nv_bfloat16*>(C);
   p.ldc = epilogue == kEpiSwiglu ? N / 2 : N;
   p.status = status;
   p.timeoutNs = 2ull * 1000 * 1000 * 1000;
   p.rank = 0; p.world = 1; p.blocksPerRank = p.tilesM;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommNone>(maps, p, ctas, s) : launch<kEpiStore, kCommNone>(maps, p, ctas, s);
+  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommNone>(maps, p, sh, s) : launch<kEpiStore, kCommNone>(maps, p, sh, s);
 }
 
 size_t purlin_tp_workspace_bytes(int world, int M, int kAg, int nRs) { return tpLayout(world, M, kAg, nRs).total; }
@@ -772,61 +889,57 @@ int purlin_tp_ag_gemm(PurlinTpContext* c, const void* xLocal, const void* W, voi
   NvtxRange range(epilogue == kEpiSwiglu ? "allGatherGemmSwiglu" : "allGatherGemm", size_t(M) * size_t(K) * 2);   // gathered bytes
   if (M > c->M || K > c->kAg || M % (c->world * kBM)) { setError("all-gather GEMM shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
-  const int ctas = ctasFor(M, M / c->world);
-  if (!fillShape(p, M, N, K, epilogue, 0, ctas)) return 1;
+  Shape sh{};
+  if (!fillShape(p, sh, M, N, K, epilogue, 0, M / c->world)) return 1;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
-  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * ctas);
+  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * sh.ctas * sh.accs);
   p.epoch = reinterpret_cast<uint64_t*>(lb); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
   p.status = reinterpret_cast<uint32_t*>(lb + 256); p.timeoutNs = c->timeoutNs;
   p.pushCounters = reinterpret_cast<uint32_t*>(lb + 4096);
-  p.pushParts = 8;
-  {
-    // Few pushing warps per CTA pace the remote stores: a saturated NVLink store queue stalls every memory
-    // instruction of its SM, the epilogue's included. PURLIN_AG_COMM_WARPS overrides (1..4).
-    const char* e = std::getenv("PURLIN_AG_COMM_WARPS");
-    p.commWarps = e ? std::min(std::max(std::atoi(e), 1), kCommWarps) : 1;
-    if (const char* pp = std::getenv("PURLIN_AG_PUSH_PARTS")) p.pushParts = std::min(std::max(std::atoi(pp), 1), 64);
-  }
+  p.pushParts = switches().agPushParts;
+  p.commWarps = switches().agCommWarps;
   p.localA = static_cast<const __nv_bfloat16*>(xLocal);
   p.C = static_cast<__nv_bfloat16*>(out); p.ldc = epilogue == kEpiSwiglu ? N / 2 : N;
   // the host cannot know the device epoch (graph replays advance it): pass the maps of both gather buffers
+  const CUtensorMap* m0 = c->maps.get(c->peers[c->rank] + c->gatherOff[0], uint64_t(M), uint64_t(K), kBM);
+  const CUtensorMap* m1 = m0 ? c->maps.get(c->peers[c->rank] + c->gatherOff[1], uint64_t(M), uint64_t(K), kBM) : nullptr;
+  const CUtensorMap* ml = m1 ? c->maps.get(xLocal, uint64_t(M / c->world), uint64_t(K), kBM) : nullptr;
+  const CUtensorMap* mb = ml ? c->maps.get(W, uint64_t(N), uint64_t(K), uint32_t(p.bn / sh.ctas)) : nullptr;
+  const CUtensorMap* mc = mb ? c->maps.get(out, uint64_t(M), uint64_t(p.ldc), 32) : nullptr;
+  if (!mc) return 1;
   Maps maps{};
-  if (!makeMap(&maps.a, c->peers[c->rank] + c->gatherOff[0], uint64_t(M), uint64_t(K), kBM)) return 1;
-  if (!makeMap(&maps.a1, c->peers[c->rank] + c->gatherOff[1], uint64_t(M), uint64_t(K), kBM)) return 1;
+  maps.a = *m0; maps.a1 = *m1; maps.aLocal = *ml; maps.b = *mb; maps.c = *mc;
   p.gatherParityBytes = c->gatherOff[1] - c->gatherOff[0];
-  if (!makeMap(&maps.aLocal, xLocal, uint64_t(M / c->world), uint64_t(K), kBM)) return 1;
-  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
   for (int q = 0; q < c->world; ++q) {
     p.gatherBuf[q] = reinterpret_cast<__nv_bfloat16*>(c->peers[q] + c->gatherOff[0]);
     p.rowReady[q] = reinterpret_cast<uint64_t*>(c->peers[q] + c->rowReadyOff);
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommAG>(maps, p, ctas, s) : launch<kEpiStore, kCommAG>(maps, p, ctas, s);
+  return epilogue == kEpiSwiglu ? launch<kEpiSwiglu, kCommAG>(maps, p, sh, s) : launch<kEpiStore, kCommAG>(maps, p, sh, s);
 }
 
 int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* out, int M, int N, int K, void* stream) {
   NvtxRange range("gemmReduceScatter", size_t(M) * size_t(N) * 2);   // bytes of the tensor that is reduce-scattered
   if (M > c->M || N > c->nRs || M % (c->world * kBM)) { setError("GEMM reduce-scatter shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
-  const int ctas = ctasFor(M, M / c->world);
-  const int scratch = std::getenv("PURLIN_RS_DIRECT_STORES") ? 0 : 1;
-  if (!fillShape(p, M, N, K, kEpiStore, 0, ctas, scratch ? kScratchBytes : 0)) return 1;
-  p.rsScratch = scratch;
+  Shape sh{};
+  if (!fillShape(p, sh, M, N, K, kEpiStore, 0, M / c->world)) return 1;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
-  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * ctas);
+  p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * sh.ctas * sh.accs);
   p.epoch = reinterpret_cast<uint64_t*>(lb + 128); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 192);
   p.status = reinterpret_cast<uint32_t*>(lb + 256); p.timeoutNs = c->timeoutNs;
   p.C = static_cast<__nv_bfloat16*>(out); p.ldc = N;
   p.partialParityStride = c->partialParityStride;
+  const CUtensorMap* ma = c->maps.get(A, uint64_t(M), uint64_t(K), kBM);
+  const CUtensorMap* mb = ma ? c->maps.get(W, uint64_t(N), uint64_t(K), uint32_t(p.bn / sh.ctas)) : nullptr;
+  if (!mb) return 1;
   Maps maps{};
-  if (!makeMap(&maps.a, A, uint64_t(M), uint64_t(K), kBM)) return 1;
-  maps.aLocal = maps.a;
-  if (!makeMap(&maps.b, W, uint64_t(N), uint64_t(K), uint32_t(p.bn / ctas))) return 1;
+  maps.a = *ma; maps.aLocal = maps.a; maps.b = *mb;
   for (int q = 0; q < c->world; ++q) {
     p.partialBuf[q] = reinterpret_cast<__nv_bfloat16*>(c->peers[q] + c->partialOff);
     p.tileReady[q] = reinterpret_cast<uint64_t*>(c->peers[q] + c->tileReadyOff);
   }
-  return launch<kEpiStore, kCommRS>(maps, p, ctas, static_cast<cudaStream_t>(stream));
+  return launch<kEpiStore, kCommRS>(maps, p, sh, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
