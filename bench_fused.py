@@ -108,14 +108,23 @@ def bench_moe(rank, world, dev, args):
     x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
     idx, w = ep.route(logits)
     y = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
-    # rows that leave this GPU (no per-destination de-duplication: one row per (token, expert) pair)
-    remote = int((idx // (E // world) != rank).sum().item())
-    rt = torch.tensor([remote], device=dev, dtype=torch.int64)
+    # Bytes that must cross NVLink: one row per (token, destination GPU) with the destination != this rank (a token
+    # routed to several experts of one GPU travels once). The count per (token, expert) pair is reported beside it.
+    epr = E // world
+    dest = idx // epr                                                       # [T, K]
+    onehot = torch.zeros(T, world, dtype=torch.bool, device=dev)
+    onehot.scatter_(1, dest.long(), True)
+    onehot[:, rank] = False
+    remote = int(onehot.sum().item())
+    remote_pairs = int((dest != rank).sum().item())
+    rt = torch.tensor([remote, remote_pairs], device=dev, dtype=torch.int64)
     if world > 1:
         dist.all_reduce(rt, op=dist.ReduceOp.MAX)
-    link_bytes = float(rt.item()) * H * 2
-    hbm_bytes = 2.0 * T * K * H * 2            # every row is read once and written once
+    link_bytes = float(rt[0].item()) * H * 2
+    pair_bytes = float(rt[1].item()) * H * 2
+    hbm_bytes = 2.0 * T * K * H * 2            # every expert row is written once on dispatch and read once on combine
     roof_us = max(link_bytes / (LINK_GBPS * 1e9), hbm_bytes / 6.5e12) * 1e6
+    pair_roof_us = max(pair_bytes / (LINK_GBPS * 1e9), hbm_bytes / 6.5e12) * 1e6
 
     def both():
         ep.dispatch(x)
@@ -140,13 +149,14 @@ def bench_moe(rank, world, dev, args):
     d_us, c_us = float(tt[0]), float(tt[1])
     emit(rank, path="MoE dispatch (+permute)", world=world, tokens_per_rank=T, hidden=H, experts=E, topk=K, us=round(d_us, 1),
          roofline_us=round(roof_us, 1), roofline_frac=round(roof_us / d_us, 3), link_GB=round(link_bytes / 1e9, 3),
-         achieved_link_GBps=round(link_bytes / d_us / 1e3, 1))
+         achieved_link_GBps=round(link_bytes / d_us / 1e3, 1), per_pair_link_GB=round(pair_bytes / 1e9, 3),
+         frac_of_per_pair_roofline=round(pair_roof_us / d_us, 3))
     emit(rank, path="MoE combine (+gate-weighted sum)", world=world, us=round(c_us, 1), roofline_us=round(roof_us, 1),
-         roofline_frac=round(roof_us / c_us, 3), achieved_link_GBps=round(link_bytes / c_us / 1e3, 1))
+         roofline_frac=round(roof_us / c_us, 3), achieved_link_GBps=round(link_bytes / c_us / 1e3, 1),
+         frac_of_per_pair_roofline=round(pair_roof_us / c_us, 3))
     emit(rank, path="MoE dispatch+combine pair", world=world, us=round(t_pair.us, 1), roofline_frac=round(2 * roof_us / t_pair.us, 3))
     # unfused baseline: sort rows by destination, NCCL all-to-all of the counts and of the rows, and back, then a weighted sum
     if world > 1:
-        epr = E // world
         flat = idx.flatten().long()
         order = torch.argsort(flat // epr * E + flat, stable=True)
         rows = x.repeat_interleave(K, dim=0)

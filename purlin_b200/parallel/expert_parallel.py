@@ -2,8 +2,10 @@
 
 ``ExpertParallelContext`` owns the symmetric receive / expert-output buffers of one process group.
 One layer is: ``route`` -> ``dispatch`` -> experts work on ``recv_rows()`` and write ``out_rows()`` -> ``combine``.
-``dispatch`` and ``combine`` must alternate (combine ends with the handshake that lets the next dispatch reuse
-the buffers).  The reference offers allToAllV only; BASELINE configuration 4 asks for this fusion.
+``dispatch`` and ``combine`` must alternate on one stream (a call out of order is refused on the device and
+``check()`` raises).  A token crosses NVLink once per destination GPU in each direction, however many of that GPU's
+experts it was routed to: the receiver fans it out to its expert rows, and the experts' GPU sends back one row per
+token, already weighted and summed over its local experts.  The reference offers allToAllV only; BASELINE configuration 4 asks for this fusion.
 """
 from __future__ import annotations
 
@@ -24,7 +26,8 @@ def _lib():
     if not _declared:
         vp, i, u64, sz = C.c_void_p, C.c_int, C.c_uint64, C.c_size_t
         lib.purlin_moe_workspace_bytes.restype = sz
-        lib.purlin_moe_workspace_bytes.argtypes = [i, i, i, i]
+        lib.purlin_moe_workspace_bytes.argtypes = [i, i, i, i, i]
+        lib.purlin_moe_plan.argtypes = [vp, vp, vp, i, vp, vp]
         lib.purlin_moe_create.restype = vp
         lib.purlin_moe_create.argtypes = [i, i, C.POINTER(u64), i, i, i, i, i, u64, vp]
         lib.purlin_moe_destroy.argtypes = [vp, vp]
@@ -55,7 +58,7 @@ class ExpertParallelContext:
         self.experts_per_rank = experts // self.world
         # balanced routing delivers max_tokens * topk rows to each rank; the factor leaves room for imbalance
         self.capacity_rows = int(max_tokens * topk * capacity_factor)
-        nbytes = int(self.lib.purlin_moe_workspace_bytes(self.world, self.capacity_rows, hidden, experts))
+        nbytes = int(self.lib.purlin_moe_workspace_bytes(self.world, max_tokens, self.capacity_rows, hidden, experts))
         if self.world > 1:
             self._owner, self._hdl, peer_ptrs, _ = allocate_symmetric(nbytes, self.device, group, provider)
         else:
@@ -89,6 +92,17 @@ class ExpertParallelContext:
         _native.check(self.lib, rc)
         return self.topk_idx[:t], self.topk_weight[:t]
 
+    def plan(self, topk_idx: torch.Tensor, topk_weight: torch.Tensor):
+        """Adopts routing the caller computed: int32 ``topk_idx`` and fp32 ``topk_weight`` of shape [tokens, topk]."""
+        t = topk_idx.shape[0]
+        if topk_idx.dtype != torch.int32 or topk_weight.dtype != torch.float32 or topk_idx.shape != (t, self.topk) or topk_weight.shape != (t, self.topk):
+            raise ValueError("routing must be int32 ids and fp32 weights of shape [tokens, topk]")
+        self.topk_idx[:t].copy_(topk_idx)
+        self.topk_weight[:t].copy_(topk_weight)
+        rc = self.lib.purlin_moe_plan(self.ctx, self.topk_idx.data_ptr(), self.topk_weight.data_ptr(), t, self.slot.data_ptr(), self.stream())
+        _native.check(self.lib, rc)
+        return self.topk_idx[:t], self.topk_weight[:t]
+
     def dispatch(self, x: torch.Tensor, blocks: int = 0):
         """Sends every token to its experts' GPUs; returns (rows in expert-major order, rows per local expert)."""
         t = x.shape[0]
@@ -119,7 +133,9 @@ class ExpertParallelContext:
         self.lib.purlin_moe_status(self.ctx, out, self.stream())
         if out[0]:
             self.lib.purlin_moe_clear_status(self.ctx, self.stream())
-            what = "receive buffer capacity exceeded" if out[0] == 6 else "a wait timed out"
+            what = {2: "receive buffer capacity exceeded", 3: "more rows for one destination than the staging area holds",
+                    7: "an expert id outside [0, experts)", 9: "dispatch called twice without a combine in between",
+                    10: "combine called without a matching dispatch"}.get(out[1], "bad plan") if out[0] == 6 else "a wait timed out"
             raise RuntimeError(f"purlin: MoE exchange failed: {what} (where {out[1]}, peer {out[2]})")
 
     def close(self):
