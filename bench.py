@@ -236,25 +236,59 @@ def _reference_arm(args, reference, rank, world):
 
 
 def collective_samples(purlin, dist, dev, world, steps):
-    """Bus GB/s of the stand-alone collectives vs NCCL at a few sizes (device-timed, max over ranks)."""
+    """Bus GB/s of the stand-alone collectives vs NCCL at a few sizes (device-timed, max over ranks), each compared
+    exactly with the NCCL result on integer-valued inputs before it is timed."""
     import torch
     from purlin_b200.utils import bench
     h = purlin.initialize(dist.group.WORLD, dev, 100, None)
+    rank = dist.get_rank()
     rows = []
-    for n in (8 << 10, 512 << 10, 32 << 20, 256 << 20):
-        x = torch.ones(n // 2, dtype=torch.bfloat16, device=dev)
-        out = torch.empty_like(x)
-        ref = x.clone()
+
+    def sample(name, key, n, ours, nccl, out, ref):
         runs = max(steps // 2, 5) if n <= (32 << 20) else 5
-        t = bench.measure(lambda: purlin.all_reduce(x, out, h, None), 5, runs)
+        out.fill_(-7)
+        ours()
+        nccl()
         purlin.check(h)
-        ok = bool(torch.all(out == world).item())
-        tn = bench.measure(lambda: dist.all_reduce(ref), 5, runs)
-        f = bench.bus_factor("ar", world)
-        rows.append({"collective": "all_reduce", "bytes": n, "us": round(t.us, 2), "busbw_GBps": round(n / t.us / 1e3 * f, 2),
-                     "nccl_us": round(tn.us, 2), "nccl_busbw_GBps": round(n / tn.us / 1e3 * f, 2), "correct": ok})
+        ok = torch.tensor([1 if torch.equal(out, ref) else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        t = bench.measure(ours, 5, runs)
+        tn = bench.measure(nccl, 5, runs)
+        f = bench.bus_factor(key, world)
+        total = bench.logical_bytes(key, n, world) if key != "ar" else n
+        rows.append({"collective": name, "bytes": total, "us": round(t.us, 2), "busbw_GBps": round(total / t.us / 1e3 * f, 2),
+                     "nccl_us": round(tn.us, 2), "nccl_busbw_GBps": round(total / tn.us / 1e3 * f, 2), "correct": bool(ok.item())})
+
+    for n in (8 << 10, 512 << 10, 32 << 20, 256 << 20):
+        x = ((torch.arange(n // 2, device=dev) + rank) % 5).to(torch.bfloat16)
+        out, ref = torch.empty_like(x), torch.empty_like(x)
+        sample("all_reduce", "ar", n, lambda: purlin.all_reduce(x, out, h, None), lambda: (ref.copy_(x), dist.all_reduce(ref)), out, ref)
+    for n in (512 << 10, 32 << 20):      # bytes per rank
+        per = n // world // 32 * 32
+        x = ((torch.arange(per // 2, device=dev) + 3 * rank) % 7).to(torch.bfloat16)
+        out, ref = torch.empty(per // 2 * world, dtype=torch.bfloat16, device=dev), torch.empty(per // 2 * world, dtype=torch.bfloat16, device=dev)
+        sample("all_gather", "ag", per, lambda: purlin.all_gather(x, out, h, None), lambda: dist.all_gather_into_tensor(ref, x), out, ref)
+        xin = ((torch.arange(per // 2 * world, device=dev) + rank) % 5).to(torch.bfloat16)
+        o2, r2 = torch.empty(per // 2, dtype=torch.bfloat16, device=dev), torch.empty(per // 2, dtype=torch.bfloat16, device=dev)
+        sample("reduce_scatter", "rs", per, lambda: purlin.reduce_scatter(xin, o2, h, None), lambda: dist.reduce_scatter_tensor(r2, xin), o2, r2)
+        o3, r3 = torch.empty_like(xin), torch.empty_like(xin)
+        sample("all_to_all", "a2a", per, lambda: purlin.all_to_all(xin, o3, h, None), lambda: dist.all_to_all_single(r3, xin), o3, r3)
     purlin.finalize(h)
     return rows
+
+
+def moe_samples(dist, dev, rank, world):
+    """MoE dispatch / combine at the DeepSeek-V3-like shape (4096 tokens per rank, hidden 7168, 256 experts, top-8):
+    microseconds and fractions of the roofline over de-duplicated NVLink bytes (device-timed, max over ranks)."""
+    import bench_fused
+
+    class A:
+        warmup, runs = 3, 10
+    bench_fused.QUIET = True
+    del bench_fused.ROWS[:]
+    bench_fused.bench_moe(rank, world, dev, A, unfused=False)
+    keep = ("path", "us", "roofline_us", "roofline_frac", "link_GB", "achieved_link_GBps", "per_pair_link_GB", "frac_of_per_pair_roofline")
+    return [{k: r[k] for k in keep if k in r} for r in bench_fused.ROWS]
 
 
 def main():
@@ -354,11 +388,40 @@ def main():
     sustained, burst, how = _peaks()
     flops = mlp.flops(T)
     tflops_per_gpu = flops / world / (ms_per_step * 1e-3) / 1e12
-    # roofline of the fused step per GPU: the slower of compute at the measured GEMM peak and NVLink bytes at 770 GB/s
+    # Roofline of the fused step per GPU: the slower of compute at the measured GEMM peak and NVLink bytes at 770 GB/s.
+    # The burst peak applies when the timed region ran without the power cap (short regions at full clock), the
+    # sustained one when the cap was active; both fractions are printed, `roofline_frac` is the one that applies.
     nvlink_bytes = (world - 1) / world * T * HIDDEN * 2 * 2 if world > 1 else 0.0   # gathered rows in + partial rows out
-    t_compute = flops / world / (sustained * 1e12)
     t_link = nvlink_bytes / 770e9
-    roofline_s = max(t_compute, t_link)
+    capped = "sw_power_cap" in clocks.summary()["reasons"]
+    frac_burst = max(flops / world / (burst * 1e12), t_link) / (ms_per_step * 1e-3)
+    frac_sustained = max(flops / world / (sustained * 1e12), t_link) / (ms_per_step * 1e-3)
+    peak_used = sustained if capped else burst
+    t_compute = flops / world / (peak_used * 1e12)
+
+    # ---- correctness of what was timed, outside the timed regions: one fused MLP output against the fp32 PyTorch
+    # reference of the same block (partial products all-reduced over the ranks)
+    fused_correct, fused_err = None, None
+    try:
+        y_chk = mlp.forward(x_dev, y).float()
+        mlp.tp.check()
+        if world > 1:
+            xs = [torch.empty_like(x_dev) for _ in range(world)]
+            dist.all_gather(xs, x_dev)
+            part = mlp.reference(torch.cat(xs))
+            dist.all_reduce(part)
+            ref = part[rank * rows_local:(rank + 1) * rows_local]
+            del part, xs
+        else:
+            ref = mlp.reference(x_dev)
+        err = (y_chk - ref).abs().max()
+        ok_t = (err <= 3e-2 * ref.abs().max() + 1e-3).to(torch.int32)
+        if world > 1:
+            dist.all_reduce(ok_t, op=dist.ReduceOp.MIN)
+        fused_correct, fused_err = bool(ok_t.item()), float(err.item())
+        del ref, y_chk
+    except Exception as e:
+        fused_correct, fused_err = False, f"{type(e).__name__}: {e}"
 
     collectives = None
     if world > 1 and not args.no_collectives:
@@ -366,6 +429,12 @@ def main():
             collectives = collective_samples(purlin, dist, dev, world, args.steps)
         except Exception as e:   # the headline number must survive a failure here
             collectives = {"error": f"{type(e).__name__}: {e}"}
+    moe = None
+    if world > 1 and not args.no_collectives:
+        try:
+            moe = moe_samples(dist, dev, rank, world)
+        except Exception as e:
+            moe = {"error": f"{type(e).__name__}: {e}"}
 
     if rank == 0:
         line = {
@@ -385,9 +454,11 @@ def main():
                        "global_batch": T, "seq_len": T, "parallelism": f"tp{world}+sp",
                        "l2": "weights read every step exceed the 126 MB L2 (no flush needed)"},
             "tflops_per_gpu": round(tflops_per_gpu, 1),
-            "roofline_frac": round(roofline_s / (ms_per_step * 1e-3), 4),
-            "roofline": {"peak_tflops": sustained, "peak_source": how + " cuBLAS bf16 sustained", "nvlink_GBps": 770,
+            "roofline_frac": round(frac_sustained if capped else frac_burst, 4),
+            "roofline": {"peak_tflops": peak_used, "peak_source": how + (" cuBLAS bf16 sustained (power cap active)" if capped else " cuBLAS bf16 burst (no power cap in the timed region)"),
+                         "frac_of_burst_peak": round(frac_burst, 4), "frac_of_sustained_peak": round(frac_sustained, 4), "nvlink_GBps": 770,
                          "compute_ms": round(t_compute * 1e3, 4), "link_ms": round(t_link * 1e3, 4)},
+            "fused_correct": fused_correct, "fused_max_abs_err": fused_err,
             "clocks": clocks.summary(),
             "e2e": {"value": round(T / (e2e_ms_per_step * 1e-3), 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms_per_step, 4),
                     "h2d_bytes_per_step": mlp._feed.h2d_bytes_per_step, "d2h_bytes_per_step": mlp._feed.d2h_bytes_per_step,
@@ -397,6 +468,8 @@ def main():
         }
         if collectives is not None:
             line["collectives"] = collectives
+        if moe is not None:
+            line["moe"] = moe
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -40,8 +40,13 @@ def peaks():
         return 1590.0, 1400.0, "fallback"
 
 
+ROWS = []      # every row emitted by this process (bench.py reads them back instead of parsing stdout)
+QUIET = False
+
+
 def emit(rank, **kw):
-    if rank == 0:
+    ROWS.append(kw)
+    if rank == 0 and not QUIET:
         print(json.dumps(kw), flush=True)
 
 
@@ -100,7 +105,7 @@ def bench_tp(rank, world, dev, args):
     tp.close()
 
 
-def bench_moe(rank, world, dev, args):
+def bench_moe(rank, world, dev, args, unfused=True):
     T, H, E, K = 4096, 7168, 256, 8
     ep = ExpertParallelContext(dist.group.WORLD if world > 1 else None, dev, max_tokens=T, hidden=H, experts=E, topk=K, capacity_factor=1.5)
     g = torch.Generator(device=dev).manual_seed(11 + rank)
@@ -156,7 +161,7 @@ def bench_moe(rank, world, dev, args):
          frac_of_per_pair_roofline=round(pair_roof_us / c_us, 3))
     emit(rank, path="MoE dispatch+combine pair", world=world, us=round(t_pair.us, 1), roofline_frac=round(2 * roof_us / t_pair.us, 3))
     # unfused baseline: sort rows by destination, NCCL all-to-all of the counts and of the rows, and back, then a weighted sum
-    if world > 1:
+    if world > 1 and unfused:
         flat = idx.flatten().long()
         order = torch.argsort(flat // epr * E + flat, stable=True)
         rows = x.repeat_interleave(K, dim=0)

@@ -72,6 +72,8 @@ size_t purlin_context_sizeof(void);
 int purlin_collective(PurlinHostContext* ctx, int collective, const void* src, void* dst, size_t bytes,
                       const size_t* sizes, const size_t* outSizes, int dtype, int reduceOp, int mode,
                       const void* policy, void* stream);
+/* Any fixed-size collective through a short signature: traits = dtype | reduceOp << 8 | mode << 16 (zero for the copy collectives). */
+int purlin_call_fixed(PurlinHostContext* ctx, int collective, const void* src, void* dst, size_t bytes, unsigned traits, void* stream);
 int purlin_all_reduce(PurlinHostContext* ctx, const void* src, void* dst, size_t bytes, int dtype, int reduceOp, int mode, void* stream);
 int purlin_all_gather(PurlinHostContext* ctx, const void* src, void* dst, size_t bytesPerRank, void* stream);
 int purlin_all_gather_v(PurlinHostContext* ctx, const void* src, void* dst, const size_t* bytesList, void* stream);

@@ -30,6 +30,7 @@ constexpr int kMaxChunks = 1024;                    // flag values reserved per 
 constexpr int kMaxCtas = 148;                       // one per B200 SM
 constexpr int kMaxSteps = 56;                       // steps in one plan (stage + local + consume + gather)
 constexpr int kCounterSlots = kMaxSteps * kMaxChunks;
+constexpr int kSeqWords = 256;                     // copies of the call sequence number: CTA b reads word b % kSeqWords
 
 // Flag value of chunk `k` (0-based) of call number `seq`. Values grow with
 // every call and every chunk, so flags are never cleared; waits compare >=.

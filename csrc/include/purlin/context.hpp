@@ -8,8 +8,10 @@
 //     consumedSignals[W] | pad to 32 B | varLenSignals[2][W] x 16 B ]
 //
 // What differs: peer pointers live inside the struct (constant-bank reads, no
-// dependent load through a device pointer table), a single call-sequence word
-// replaces per-CTA epochs, and a status word receives bounded-wait timeouts.
+// dependent load through a device pointer table), one call-sequence number kept in
+// kSeqWords identical words (every CTA reads its own and advances its share when it
+// leaves, so no CTA waits for another at the end of a call) replaces per-CTA epochs,
+// and a status word receives bounded-wait timeouts.
 #pragma once
 #include "constants.hpp"
 
@@ -50,9 +52,9 @@ struct Context {
   unsigned char* mcStagingTR;            // NVLS multicast alias of stagingTR, or null
   unsigned char* mcStagingLR;            // NVLS multicast alias of stagingLR, or null
   // local (not symmetric)
-  uint64_t* seq;                         // call sequence number; half = seq & 1
+  uint64_t* seq;                         // [kSeqWords] call sequence number, the same in every word between calls; half = seq & 1
   uint32_t* counters;                    // [kCounterSlots] last-arrival counters, self-resetting
-  uint32_t* exitCounter;                 // CTAs that finished the running call
+  uint32_t* exitCounter;                 // CTAs that finished the running call (used only while tracing: the last one stamps the end)
   uint32_t* status;                      // [4]: code, step, peer, chunk
   uint64_t* trace;                       // optional ring of kTraceSlots x {start ns, end ns, payload bytes, collective}; null = off
   size_t stagingTRSize;

@@ -114,7 +114,23 @@ struct Policy {
   int32_t weighted = 1;         // apportion CTAs by stream size in V collectives
   uint64_t chunkBytes = 0;      // 0: one flag per stream
   uint64_t perStreamThreshold = 128ull << 10;
+  int32_t maxCtas = 0;          // > 0: the plan may use at most this many CTAs (the collective shares the GPU with other work)
+  int32_t reserved = 0;
 };
+
+// Shrinks the CTA counts of a policy so that a plan built from it fits `budget` CTAs, given that the plan built from the
+// unshrunk policy needed `needed`. The reference caps every collective at 64 CTAs (csrc/include/purlin/constants.cuh:21)
+// so that it can run beside compute kernels; here the cap is a knob (0 = the whole GPU).
+inline void shrinkToBudget(Policy& p, int needed, int budget, int world) {
+  if (budget <= 0 || needed <= budget) return;
+  auto scale = [&](int32_t& v, int floorAt) { v = std::max<int32_t>(int32_t(int64_t(v) * budget / needed), floorAt); };
+  const int peers = std::max(world - 1, 1);
+  scale(p.putBlocks, 1);
+  scale(p.localBlocks, 1);
+  scale(p.consumeBlocks, peers);
+  scale(p.gatherBlocks, peers);
+  scale(p.lrBlocks, 1);
+}
 
 struct CollectiveSpec {
   CollectiveType type = CollectiveType::allReduce;

@@ -6,7 +6,7 @@
 // protocol). Here the derivation is a run-time function (layout.hpp) whose
 // output is this struct: a list of steps, each bound to a range of CTAs. The
 // same plan is executed by the sm_100a kernels (snac.cuh), by the CPU
-// interpreter (cpu_sim.cpp) and by the gloo path of the Python package, so the
+// interpreter (host_core.cpp) and by the gloo path of the Python package, so the
 // protocol can be tested without a GPU.
 #pragma once
 #include "constants.hpp"
@@ -69,7 +69,10 @@ struct Step {
   uint32_t counterBase; // first last-arrival counter of this step
 };
 
-struct Plan {
+// N = kMaxSteps for the general plan; kCompactSteps for the short plans of the latency regime, which travel as kernel
+// parameters in a quarter of the bytes (the header is the same, so the executor is one template over both).
+template <int N>
+struct PlanT {
   int32_t collective;   // CollectiveType, for reports
   int32_t regime;       // Regime
   int32_t consumeOp;    // ConsumeOp
@@ -86,8 +89,20 @@ struct Plan {
   int32_t reserved;
   uint64_t smemBytes;
   uint64_t payloadBytes;  // logical bytes for reports
-  Step steps[kMaxSteps];
+  Step steps[N];
 };
+using Plan = PlanT<kMaxSteps>;
+constexpr int kCompactSteps = 16;
+using PlanCompact = PlanT<kCompactSteps>;
+
+// The first steps of a plan that has at most kCompactSteps of them.
+inline void compactPlan(const Plan& in, PlanCompact& out) {
+  out.collective = in.collective; out.regime = in.regime; out.consumeOp = in.consumeOp; out.reduceOp = in.reduceOp;
+  out.dtype = in.dtype; out.deterministic = in.deterministic; out.blocks = in.blocks; out.threads = in.threads;
+  out.nSteps = in.nSteps; out.varLenArrival = in.varLenArrival; out.mmDepth = in.mmDepth; out.unroll = in.unroll;
+  out.stageDepth = in.stageDepth; out.reserved = in.reserved; out.smemBytes = in.smemBytes; out.payloadBytes = in.payloadBytes;
+  for (int i = 0; i < kCompactSteps; ++i) out.steps[i] = in.steps[i];
+}
 
 // Aligned even split with the remainder spread over the first parts
 // (behaviour of partition<Align>, csrc/include/purlin/partition.cuh:217-247).

@@ -333,11 +333,11 @@ PURLIN_D bool awaitArrival(const Context& ctx, const Frame& f) {
 
 // One CTA's share of a whole collective. `bIdx`/`blocks` are the CTA's index and the
 // grid size of this rank (not of the launch: emulation stacks ranks along grid.y).
-template <class Atom, DType T, ReduceOp Op, bool Reduces>
-PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src, unsigned char* dst,
+template <class Atom, DType T, ReduceOp Op, bool Reduces, class PlanType = Plan>
+PURLIN_D void run(const Context& ctx, const PlanType& plan, const unsigned char* src, unsigned char* dst,
                   int bIdx, int blocks, const unsigned char** peerPtr, unsigned char* dynSmem) {
   Frame f;
-  f.seq = sig::ldRelaxedSys(ctx.seq);
+  f.seq = sig::ldRelaxedSys(ctx.seq + (bIdx % kSeqWords));
   f.half = int(f.seq & 1);
   f.bIdx = bIdx;
   f.src = src;
@@ -346,7 +346,13 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
   f.mmDepth = plan.mmDepth;
   f.bulkDepth = plan.regime == int32_t(Regime::throughput) ? plan.stageDepth : 0;
   f.smem = dynSmem;
-  bool ok = !sig::failed(ctx);    // a context that failed stays quiet until the host clears it
+  // A context that failed stays quiet until the host clears it. The status word is requested here and looked at after
+  // the CTA's first step has issued its own loads, so that its latency overlaps theirs instead of preceding them (a
+  // small collective is a chain of a few memory round trips; this removes one). The first step of a latency plan only
+  // sends this rank's own input, which is harmless on a failed context.
+  const uint32_t statusAtEntry = sig::ldRelaxedGpu32(ctx.status);
+  bool ok = true;
+  bool checkedStatus = false;
   if (ctx.trace != nullptr && bIdx == 0 && threadIdx.x == 0) {
     // device-side timing: the first CTA stamps the start of call `seq`, the last CTA out stamps its end
     uint64_t* rec = ctx.trace + (f.seq % uint64_t(kTraceSlots)) * 4;
@@ -358,6 +364,7 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
   for (int si = 0; si < plan.nSteps && ok; ++si) {
     const Step& s = plan.steps[si];
     if (bIdx < s.blockBegin || bIdx >= s.blockBegin + s.blockCount) continue;
+    if (!checkedStatus && s.role != kRolePacketPut) { checkedStatus = true; if (statusAtEntry != 0u) { ok = false; break; } }
     switch (s.role) {
       case kRoleStage: ok = stage<Atom>(ctx, s, si, f); break;
       case kRoleLocal: local<Atom>(ctx, s, f); break;
@@ -375,14 +382,15 @@ PURLIN_D void run(const Context& ctx, const Plan& plan, const unsigned char* src
     }
   }
   if (ok && plan.varLenArrival && bIdx == 0) ok = awaitArrival(ctx, f);
-  // the last CTA out advances the call sequence; the next launch (stream order) reads it
+  // Every CTA advances its share of the sequence words when it leaves; the next launch (stream order) finds them all
+  // advanced. Nobody waits for the last CTA. (A traced context also counts the CTAs out: the last one stamps the end.)
   __syncthreads();
-  if (threadIdx.x == 0) {
+  for (int w = bIdx + int(threadIdx.x) * blocks; w < kSeqWords; w += blocks * int(blockDim.x)) ctx.seq[w] = f.seq + 1;
+  if (ctx.trace != nullptr && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(ctx.exitCounter, 1u) == uint32_t(blocks - 1)) {
       *ctx.exitCounter = 0;
-      if (ctx.trace != nullptr) ctx.trace[(f.seq % uint64_t(kTraceSlots)) * 4 + 1] = sig::globalTimerNs();
-      *ctx.seq = f.seq + 1;
+      ctx.trace[(f.seq % uint64_t(kTraceSlots)) * 4 + 1] = sig::globalTimerNs();
       __threadfence();
     }
   }

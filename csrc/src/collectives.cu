@@ -28,6 +28,7 @@ void setError(const std::string& e);
 bool makeSpec(CollectiveSpec& s, int collective, int world, int rank, size_t bytes, const size_t* sizes, const size_t* outSizes,
               int dtype, int reduceOp, int mode, int multicastAvailable, int inPlace);
 bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen);
+int maxCtasSetting();
 }  // namespace purlin
 
 using namespace purlin;
@@ -42,6 +43,7 @@ struct PurlinHostContext {
   // plans of fixed-size calls under the table/default policy, keyed by (collective, bytes, dtype, op, mode, in-place)
   std::unordered_map<uint64_t, Plan> planCache;
   size_t planCacheTableSize = 0;
+  int planCacheBudget = 0;      // the CTA budget the cached plans were built under
 };
 
 namespace {
@@ -62,6 +64,16 @@ snacKernel(const __grid_constant__ Context ctx, const __grid_constant__ Plan pla
   __shared__ const unsigned char* peerPtr[kMaxRanks];
   extern __shared__ __align__(128) unsigned char dynSmem[];
   snac::run<Atom, T, Op, Reduces>(ctx, plan, src, dst, blockIdx.x, gridDim.x, peerPtr, dynSmem);
+}
+
+// The same executor on a plan of at most kCompactSteps steps (every latency-regime plan up to eight ranks): the launch
+// carries about 2 KB of parameters instead of 5 KB.
+template <DType T, ReduceOp Op, bool Reduces>
+__global__ void __launch_bounds__(kMaxThreads, 1)
+snacKernelCompact(const __grid_constant__ Context ctx, const __grid_constant__ PlanCompact plan, const unsigned char* src, unsigned char* dst) {
+  __shared__ const unsigned char* peerPtr[kMaxRanks];
+  extern __shared__ __align__(128) unsigned char dynSmem[];
+  snac::run<Atom, T, Op, Reduces, PlanCompact>(ctx, plan, src, dst, blockIdx.x, gridDim.x, peerPtr, dynSmem);
 }
 
 // Emulation launch: grid.y virtual ranks on one GPU (cooperative, so all CTAs are resident
@@ -98,7 +110,16 @@ __global__ void __launch_bounds__(kMaxThreads, 1) p2pKernel(unsigned char* dst, 
 }
 
 using ProdFn = void (*)(const Context, const Plan, const unsigned char*, unsigned char*);
+using CompactFn = void (*)(const Context, const PlanCompact, const unsigned char*, unsigned char*);
 using EmuFn = void (*)(const EmuRank*);
+
+template <DType T> CompactFn compactByOp(int op) {
+  switch (ReduceOp(op)) {
+    case ReduceOp::add: return snacKernelCompact<T, ReduceOp::add, true>;
+    case ReduceOp::mul: return snacKernelCompact<T, ReduceOp::mul, true>;
+    default: return snacKernelCompact<T, ReduceOp::max, true>;
+  }
+}
 
 template <DType T> ProdFn prodByOp(int op) {
   switch (ReduceOp(op)) {
@@ -122,6 +143,16 @@ ProdFn prodKernel(const Plan& p) {
     case DType::fp8e4m3: return prodByOp<DType::fp8e4m3>(p.reduceOp);
     case DType::fp8e5m2: return prodByOp<DType::fp8e5m2>(p.reduceOp);
     default: return prodByOp<DType::fp32>(p.reduceOp);
+  }
+}
+CompactFn compactKernel(const Plan& p) {
+  if (p.consumeOp == int32_t(ConsumeOp::copy)) return snacKernelCompact<DType::fp32, ReduceOp::add, false>;
+  switch (DType(p.dtype)) {
+    case DType::bf16: return compactByOp<DType::bf16>(p.reduceOp);
+    case DType::fp16: return compactByOp<DType::fp16>(p.reduceOp);
+    case DType::fp8e4m3: return compactByOp<DType::fp8e4m3>(p.reduceOp);
+    case DType::fp8e5m2: return compactByOp<DType::fp8e5m2>(p.reduceOp);
+    default: return compactByOp<DType::fp32>(p.reduceOp);
   }
 }
 EmuFn emuKernel(const Plan& p) {
@@ -162,8 +193,15 @@ bool ensureSmemOptIn(const void* fn) {
 }
 
 int launchPlan(PurlinHostContext* h, const Plan& plan, const void* src, void* dst, cudaStream_t stream) {
-  ProdFn fn = prodKernel(plan);
   const int threads = std::min(std::max(plan.threads, 32), kMaxThreads);
+  if (plan.nSteps <= kCompactSteps && plan.smemBytes == 0) {
+    PlanCompact small;
+    compactPlan(plan, small);
+    compactKernel(plan)<<<plan.blocks, threads, 0, stream>>>(h->dev, small, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst));
+    CUDA_OK(cudaGetLastError());
+    return 0;
+  }
+  ProdFn fn = prodKernel(plan);
   if (plan.smemBytes > 0 && !ensureSmemOptIn(reinterpret_cast<const void*>(fn))) { setError("cannot opt in to the bulk ring's shared memory"); return 1; }
   fn<<<plan.blocks, threads, plan.smemBytes, stream>>>(h->dev, plan, static_cast<const unsigned char*>(src), static_cast<unsigned char*>(dst));
   CUDA_OK(cudaGetLastError());
@@ -209,15 +247,17 @@ PurlinHostContext* purlin_context_create(int rank, int world, const uint64_t* pe
     if (std::getenv("PURLIN_DISABLE_MULTIMEM_LR") == nullptr) c.mcStagingLR = c.mcStagingTR + h->ws.lrOffset;
   }
   h->hasMulticast = c.mcStagingTR != nullptr;
-  const size_t localBytes = 256 + size_t(kCounterSlots) * 4;
+  // local block: [0, 2048) sequence words, [2048] exit counter, [2112] status, [4096, ...) last-arrival counters
+  const size_t localBytes = 4096 + size_t(kCounterSlots) * 4;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (cudaMalloc(&h->localBlock, localBytes) != cudaSuccess) { delete h; setError("cudaMalloc of the local counters failed"); return nullptr; }
   cudaMemsetAsync(h->localBlock, 0, localBytes, s);
   unsigned char* lb = static_cast<unsigned char*>(h->localBlock);
+  static_assert(kSeqWords * 8 <= 2048, "sequence words overlap the exit counter");
   c.seq = reinterpret_cast<uint64_t*>(lb);
-  c.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
-  c.status = reinterpret_cast<uint32_t*>(lb + 128);
-  c.counters = reinterpret_cast<uint32_t*>(lb + 256);
+  c.exitCounter = reinterpret_cast<uint32_t*>(lb + 2048);
+  c.status = reinterpret_cast<uint32_t*>(lb + 2112);
+  c.counters = reinterpret_cast<uint32_t*>(lb + 4096);
   if (const char* t = std::getenv("PURLIN_TRACE"); t && t[0] != '0') {
     // opt-in: every call leaves {start, end, bytes, collective} in a ring of kTraceSlots records (purlin_context_trace)
     if (cudaMalloc(&h->traceRing, size_t(kTraceSlots) * 32) != cudaSuccess) { cudaFree(h->localBlock); delete h; setError("cudaMalloc of the trace ring failed"); return nullptr; }
@@ -312,7 +352,9 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
   }
   if (!forced && !variable && bytes < (1ull << 40)) {
     // the layout engine is deterministic in these inputs: build each plan once
-    if (h->planCacheTableSize != TuningTable::global().size()) { h->planCache.clear(); h->planCacheTableSize = TuningTable::global().size(); }
+    if (h->planCacheTableSize != TuningTable::global().size() || h->planCacheBudget != maxCtasSetting()) {
+      h->planCache.clear(); h->planCacheTableSize = TuningTable::global().size(); h->planCacheBudget = maxCtasSetting();
+    }
     const uint64_t key = (uint64_t(bytes) << 16) ^ (uint64_t(collective) << 12) ^ (uint64_t(dtype) << 8) ^ (uint64_t(reduceOp) << 4) ^
                          (uint64_t(mode) << 1) ^ uint64_t(src == dst && src != nullptr);
     auto it = h->planCache.find(key);
@@ -327,6 +369,12 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
   Plan plan;
   if (!planFor(spec, h->ws, forced, plan, nullptr)) return 1;
   return launchPlan(h, plan, src, dst, s);
+}
+
+// The fixed-size collectives through one short signature (seven scalar arguments: what a foreign-function call from
+// Python pays for is mostly the argument count). traits = dtype | reduceOp << 8 | mode << 16.
+int purlin_call_fixed(PurlinHostContext* h, int collective, const void* src, void* dst, size_t bytes, unsigned traits, void* stream) {
+  return purlin_collective(h, collective, src, dst, bytes, nullptr, nullptr, int(traits & 0xffu), int((traits >> 8) & 0xffu), int((traits >> 16) & 0xffu), nullptr, stream);
 }
 
 int purlin_all_reduce(PurlinHostContext* h, const void* src, void* dst, size_t bytes, int dtype, int reduceOp, int mode, void* stream) {

@@ -8,7 +8,9 @@
 // back-pressure, so protocol errors (a wait nobody satisfies, a slot reused too
 // early, a byte produced twice or never) show up without a GPU. A rank can be
 // made absent to check that the others report a time-out instead of hanging.
+#include <atomic>
 #include <cmath>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <memory>
@@ -77,17 +79,41 @@ static bool buildChecked(const CollectiveSpec& s, const Policy& p, const Workspa
   return true;
 }
 
+// Process-wide CTA budget of a collective (0 = none): PURLIN_MAX_CTAS in the environment, or purlin_set_max_ctas().
+static std::atomic<int> g_maxCtas{-1};
+int maxCtasSetting() {
+  int v = g_maxCtas.load();
+  if (v < 0) {
+    const char* e = std::getenv("PURLIN_MAX_CTAS");
+    v = e ? std::max(std::atoi(e), 0) : 0;
+    g_maxCtas.store(v);
+  }
+  return v;
+}
+
+// build under a CTA budget: shrink the policy's CTA counts until the plan fits (a plan needs a few CTAs per peer at least)
+static bool buildWithinBudget(const CollectiveSpec& s, Policy& p, const WorkspaceLayout& ws, Plan& plan, std::string& err) {
+  const int budget = p.maxCtas > 0 ? p.maxCtas : maxCtasSetting();
+  bool ok = buildChecked(s, p, ws, plan, err);
+  for (int attempt = 0; ok && budget > 0 && plan.blocks > budget && attempt < 6; ++attempt) {
+    shrinkToBudget(p, plan.blocks, budget - attempt, s.world);
+    ok = buildChecked(s, p, ws, plan, err);
+  }
+  if (ok && budget > 0 && plan.blocks > budget) { err = "the collective cannot run in " + std::to_string(budget) + " CTAs at this world size"; return false; }
+  return ok;
+}
+
 bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen) {
   std::string err;
   Policy p = forced ? *forced : selectPolicy(s, ws);
-  bool ok = buildChecked(s, p, ws, plan, err);
+  bool ok = buildWithinBudget(s, p, ws, plan, err);
   if (!ok && !forced) {   // a measured band may not fit this call (uneven V sizes): fall back to built-in choices
     std::string err2;
     p = defaultPolicy(s, ws);
-    ok = buildChecked(s, p, ws, plan, err2);
+    ok = buildWithinBudget(s, p, ws, plan, err2);
     if (!ok && p.regime == int32_t(Regime::latency)) {
       p.regime = int32_t(Regime::throughput);
-      ok = buildChecked(s, p, ws, plan, err2);
+      ok = buildWithinBudget(s, p, ws, plan, err2);
     }
     if (!ok) err = err2;
   }
@@ -161,6 +187,9 @@ int purlin_tuning_add(int collective, int world, uint64_t maxBytes, const void* 
   return 0;
 }
 size_t purlin_tuning_size(void) { return TuningTable::global().size(); }
+// CTA budget of every collective planned from now on by this process (0 = the whole GPU); returns the previous value.
+int purlin_set_max_ctas(int maxCtas) { const int old = maxCtasSetting(); g_maxCtas.store(maxCtas > 0 ? maxCtas : 0); return old; }
+int purlin_get_max_ctas(void) { return maxCtasSetting(); }
 
 // MoE routing of `tokens` rows on the host: the arithmetic of the routing kernels (moe_route.cuh), total for any input.
 int purlin_moe_route_host(const float* logits, int tokens, int experts, int topk, int normalize, int32_t* topkIdx, float* topkWeight) {

@@ -113,8 +113,15 @@ def workspace_layout(world: int, staging_size: int = STAGING_BUFFER_SIZE) -> dic
     return dict(zip(names, [int(v) for v in out]))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream(stream_ptr: Optional[int]) -> int:
+    """The caller's stream handle, or the current stream of the current device (about a tenth of the cost of building a
+    ``torch.cuda.Stream`` object per call, which matters for the launch-bound small collectives)."""
     if stream_ptr is None:
+        if _raw_stream is not None:
+            return _raw_stream(torch.cuda.current_device())
         return torch.cuda.current_stream().cuda_stream
     return int(stream_ptr)
 
@@ -226,7 +233,7 @@ def _nbytes(t: torch.Tensor) -> int:
 
 
 def _mode(m) -> int:
-    return int(ReductionMode(m))
+    return m if (m == 0 or m == 1) and type(m) is int else int(ReductionMode(m))
 
 
 def _call(handle, collective, src, dst, nbytes, sizes, out_sizes, dtype, op, mode, stream_ptr, policy=None):
@@ -242,9 +249,24 @@ def _call(handle, collective, src, dst, nbytes, sizes, out_sizes, dtype, op, mod
     _native.check(handle.mod, rc)
 
 
+def _call_fixed(handle, collective: int, src, dst, nbytes: int, traits: int, stream_ptr, policy):
+    """The launch-bound path of the fixed-size collectives: the fewest Python operations and the shortest native
+    signature that do the job (a small collective costs about as much on the host as on the device)."""
+    if policy is not None or handle.cpu is not None or handle.ctx is None:
+        return _call(handle, collective, src, dst, nbytes, None, None, traits & 0xff, (traits >> 8) & 0xff, traits >> 16, stream_ptr, policy)
+    if not (src.is_contiguous() and dst.is_contiguous()):
+        raise ValueError("purlin collectives need contiguous tensors")
+    mod = handle.mod
+    if mod.purlin_call_fixed(handle.ctx, collective, src.data_ptr(), dst.data_ptr(), nbytes, traits,
+                             stream_ptr if stream_ptr is not None else _stream(None)):
+        _native.check(mod, 1)
+
+
+_AR, _AG, _RS, _A2A = int(Collective.ALL_REDUCE), int(Collective.ALL_GATHER), int(Collective.REDUCE_SCATTER), int(Collective.ALL_TO_ALL)
+
+
 def all_gather(in_tensor, out_tensor, handle, stream_ptr=None, policy=None):
-    _contig(in_tensor, out_tensor)
-    _call(handle, Collective.ALL_GATHER, in_tensor, out_tensor, _nbytes(in_tensor), None, None, 0, 0, 0, stream_ptr, policy)
+    _call_fixed(handle, _AG, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size(), 0, stream_ptr, policy)
 
 
 def all_gather_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, stream_ptr=None, policy=None):
@@ -256,15 +278,13 @@ def all_gather_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, strea
 
 def all_reduce(in_tensor, out_tensor, handle, stream_ptr=None, reduction_mode=ReductionMode.NON_DETERMINISTIC,
                op: ReduceOp = ReduceOp.ADD, policy=None):
-    _contig(in_tensor, out_tensor)
-    _call(handle, Collective.ALL_REDUCE, in_tensor, out_tensor, _nbytes(in_tensor), None, None,
-          buffer_type(in_tensor.dtype), op, _mode(reduction_mode), stream_ptr, policy)
+    _call_fixed(handle, _AR, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size(),
+                int(buffer_type(in_tensor.dtype)) | (int(op) << 8) | (_mode(reduction_mode) << 16), stream_ptr, policy)
 
 
 def all_to_all(in_tensor, out_tensor, handle, stream_ptr=None, policy=None):
     """``in_tensor`` holds one equal slice per peer; the native call takes bytes per slice (total // world)."""
-    _contig(in_tensor, out_tensor)
-    _call(handle, Collective.ALL_TO_ALL, in_tensor, out_tensor, _nbytes(in_tensor) // handle.world, None, None, 0, 0, 0, stream_ptr, policy)
+    _call_fixed(handle, _A2A, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size() // handle.world, 0, stream_ptr, policy)
 
 
 def all_to_all_v(in_tensor, out_tensor, splits: Sequence[int], handle, stream_ptr=None, policy=None):
@@ -278,9 +298,8 @@ def all_to_all_v(in_tensor, out_tensor, splits: Sequence[int], handle, stream_pt
 
 def reduce_scatter(in_tensor, out_tensor, handle, stream_ptr=None, reduction_mode=ReductionMode.NON_DETERMINISTIC,
                    op: ReduceOp = ReduceOp.ADD, policy=None):
-    _contig(in_tensor, out_tensor)
-    _call(handle, Collective.REDUCE_SCATTER, in_tensor, out_tensor, _nbytes(in_tensor) // handle.world, None, None,
-          buffer_type(in_tensor.dtype), op, _mode(reduction_mode), stream_ptr, policy)
+    _call_fixed(handle, _RS, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size() // handle.world,
+                int(buffer_type(in_tensor.dtype)) | (int(op) << 8) | (_mode(reduction_mode) << 16), stream_ptr, policy)
 
 
 def reduce_scatter_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, stream_ptr=None,
@@ -290,6 +309,17 @@ def reduce_scatter_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, s
         raise ValueError("bytes_list needs one entry per rank")
     _call(handle, Collective.REDUCE_SCATTER_V, in_tensor, out_tensor, 0, list(bytes_list), None,
           buffer_type(in_tensor.dtype), op, _mode(reduction_mode), stream_ptr, policy)
+
+
+def set_max_ctas(max_ctas: int) -> int:
+    """CTA budget of every collective planned from now on in this process (0 = the whole GPU, the default; the reference
+    caps its collectives at 64 so that they can run beside compute kernels). Returns the previous value. The environment
+    variable ``PURLIN_MAX_CTAS`` sets the initial value."""
+    old = 0
+    for lib in (_native.host(), _native.cuda() if torch.cuda.is_available() else None):
+        if lib is not None:
+            old = int(lib.purlin_set_max_ctas(int(max_ctas)))
+    return old
 
 
 def build_plan(collective, world, rank, nbytes=0, sizes=None, out_sizes=None, dtype=DataType.BF16, op=ReduceOp.ADD,

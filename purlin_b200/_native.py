@@ -53,6 +53,7 @@ class Policy(C.Structure):
         ("mmDepth", C.c_int32), ("unroll", C.c_int32), ("stageDepth", C.c_int32), ("arPath", C.c_int32),
         ("lrMulticast", C.c_int32), ("weighted", C.c_int32),
         ("chunkBytes", C.c_uint64), ("perStreamThreshold", C.c_uint64),
+        ("maxCtas", C.c_int32), ("reserved", C.c_int32),
     ]
 
     def as_dict(self):
@@ -128,6 +129,7 @@ def cuda():
         lib.purlin_context_has_multicast.argtypes = [vp]
         lib.purlin_context_sizeof.restype = sz
         lib.purlin_collective.argtypes = [vp, i, vp, vp, sz, vp, vp, i, i, i, vp, vp]
+        lib.purlin_call_fixed.argtypes = [vp, i, vp, vp, sz, C.c_uint, vp]
         lib.purlin_all_reduce.argtypes = [vp, vp, vp, sz, i, i, i, vp]
         lib.purlin_all_gather.argtypes = [vp, vp, vp, sz, vp]
         lib.purlin_all_gather_v.argtypes = [vp, vp, vp, vp, vp]

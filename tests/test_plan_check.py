@@ -190,3 +190,27 @@ def test_in_place_reduce_scatter_and_all_to_all_are_refused(coll):
     with pytest.raises(RuntimeError, match="in place"):
         P.build_plan(coll, 4, 2, 0 if sizes else 4096, sizes=sizes, out_sizes=outs, in_place=True)
     P.build_plan(coll, 4, 2, 0 if sizes else 4096, sizes=sizes, out_sizes=outs, in_place=False)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_cta_budget_is_honoured_by_every_collective(world):
+    """With a budget of 64 CTAs (the reference's cap) every plan fits it, and the interpreter still gets exact results."""
+    import torch
+    from helpers import sim
+    old = P.set_max_ctas(64)
+    try:
+        for coll in (AR, AG, RS, A2A):
+            for size in (8 << 10, 512 << 10, 4 << 20, 64 << 20, 256 << 20):
+                size = size // (32 * world) * (32 * world)
+                for mc in (False, True):
+                    plan, _ = P.build_plan(coll, world, 1, size, multicast=mc)
+                    assert plan.blocks <= 64, (int(coll), world, size, mc, plan.blocks)
+        for coll in (AR, AG, RS, A2A):
+            status, outs, exp = sim(coll, world, 32 * world * 40, None, dtype=4)
+            assert status[0] == 0
+            for r in range(world):
+                assert torch.equal(outs[r], exp[r])
+    finally:
+        P.set_max_ctas(old)
+    plan, _ = P.build_plan(AR, world, 0, 64 << 20)
+    assert P.set_max_ctas(0) == 0

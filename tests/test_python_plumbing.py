@@ -26,6 +26,10 @@ class RecordingLib:
                                dtype=int(dtype), op=int(op), mode=int(mode), policy=policy, stream=stream))
         return 0
 
+    def purlin_call_fixed(self, ctx, coll, src, dst, nbytes, traits, stream):
+        # the short signature of the fixed-size collectives: traits = dtype | op << 8 | mode << 16
+        return self.purlin_collective(ctx, coll, src, dst, nbytes, None, None, traits & 0xff, (traits >> 8) & 0xff, traits >> 16, None, stream)
+
     def purlin_context_create(self, rank, world, ptrs, mc, staging, timeout, stream):
         self.calls.append(dict(create=True, rank=rank, world=world, ptrs=list(ptrs), mc=mc, staging=staging, stream=stream))
         return 0xC0FFEE
