@@ -38,6 +38,7 @@ struct Frame {
   unsigned char* dst;
   int unroll;
   int mmDepth;
+  bool wideReduce;
   int bulkDepth;            // > 0: copy roles stream through the bulk-async ring in `smem`
   unsigned char* smem;
 };
@@ -85,6 +86,12 @@ struct StageHooks {
   PURLIN_D bool beforeStore(uint32_t k) const {
     if (!(s.flags & kFlagCyclic) || k < s.slots) return true;
     const uint64_t need = flagValue(f.seq, k - s.slots);      // every reader drained the slot's previous tenant
+    if (s.flags & kFlagDrainGather) {
+      if (s.peer != ctx.rank) return sig::waitAtLeast(ctx, ctx.gatherSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k);
+      for (int q = 0; q < ctx.world; ++q)
+        if (q != ctx.rank && !sig::waitAtLeast(ctx, ctx.consumedSignals[ctx.rank] + q, need, kStatusTimeoutSignal, si, q, k)) return false;
+      return true;
+    }
     if (s.peer >= 0) return sig::waitAtLeast(ctx, ctx.consumedSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k);
     for (int q = 0; q < ctx.world; ++q) {
       if (q == ctx.rank && !(s.flags & kFlagDrainSelf)) continue;
@@ -155,9 +162,18 @@ PURLIN_D bool stage(const Context& ctx, const Step& s, int si, const Frame& f) {
     if ((s.flags & kFlagCyclic) && k >= s.slots) {
       // back-pressure: every reader of this slot must have drained its previous tenant
       const uint64_t need = flagValue(f.seq, k - s.slots);
-      const bool ok = s.peer >= 0
-          ? ctaWait(ctx, ctx.consumedSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k)
-          : ctaWaitAll(ctx, ctx.consumedSignals, ctx.rank, need, (s.flags & kFlagDrainSelf) == 0, kStatusTimeoutSignal, si, k);
+      bool ok;
+      if (s.flags & kFlagDrainGather) {
+        // composed all-reduce: a peer's window is free once that peer has reduced the chunk; this rank's own window
+        // (the seam) once every peer has gathered the reduced chunk out of it
+        ok = s.peer != ctx.rank
+            ? ctaWait(ctx, ctx.gatherSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k)
+            : ctaWaitAll(ctx, ctx.consumedSignals, ctx.rank, need, true, kStatusTimeoutSignal, si, k);
+      } else {
+        ok = s.peer >= 0
+            ? ctaWait(ctx, ctx.consumedSignals[ctx.rank] + s.peer, need, kStatusTimeoutSignal, si, s.peer, k)
+            : ctaWaitAll(ctx, ctx.consumedSignals, ctx.rank, need, (s.flags & kFlagDrainSelf) == 0, kStatusTimeoutSignal, si, k);
+      }
       if (!ok) return false;
     }
     superCopy<Atom>(staging + slotOff(s, k), f.src + s.srcOff + size_t(k) * s.chunkBytes, chunkLen(s, k), j, n, f.unroll);
@@ -219,7 +235,7 @@ PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, 
       if (s.flags & kFlagMulticastOut) a.mcSeam = ctx.mcStagingTR + so;
       else a.seam = ctx.stagingTR[ctx.rank] + so;
     }
-    if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth);
+    if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth, f.wideReduce);
     if (s.flags & (kFlagNotifyGather | kFlagCyclic)) {
       if (s.flags & kFlagMulticastOut) __threadfence_system();
       if (ctaLastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n) && int(threadIdx.x) < ctx.world) {
@@ -252,6 +268,18 @@ PURLIN_D void packetPut(const Context& ctx, const Step& s, const Frame& f) {
   const uint64_t* src = reinterpret_cast<const uint64_t*>(f.src + s.srcOff);
   const uint64_t flag = flagValue(f.seq, 0);
   const size_t first = s.dstOff / 8;
+  if (s.peer < 0 && !(s.flags & kFlagMulticastOut) && ctx.world > 2 && words * size_t(ctx.world - 1) <= 2 * stride) {
+    // Peer-striped: with few words and many peers, (word, peer) pairs are spread over the threads, so that every
+    // store to a peer is some thread's first and only one instead of the last of W - 1 issued in a row
+    // (the one-warp-per-peer latency stage of the reference, csrc/include/purlin/snac.cuh:1672-1688).
+    const size_t pairs = words * size_t(ctx.world - 1);
+    for (size_t idx = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; idx < pairs; idx += stride) {
+      const size_t i = idx % words;
+      const int q = 1 + int(idx / words);
+      pkt::write(slotOf(ctx, (ctx.rank + q) % ctx.world, ctx.rank, f.half, false) + first + i, src[i], flag);
+    }
+    return;
+  }
   for (size_t i = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; i < words; i += stride) {
     const uint64_t v = src[i];
     if (s.peer >= 0) {
@@ -344,6 +372,7 @@ PURLIN_D void run(const Context& ctx, const PlanType& plan, const unsigned char*
   f.dst = dst;
   f.unroll = plan.unroll;
   f.mmDepth = plan.mmDepth;
+  f.wideReduce = plan.wideReduce != 0;
   f.bulkDepth = plan.regime == int32_t(Regime::throughput) ? plan.stageDepth : 0;
   f.smem = dynSmem;
   // A context that failed stays quiet until the host clears it. The status word is requested here and looked at after

@@ -337,9 +337,13 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
   const bool variable = isVariable(spec.in);
   if (!variable && bytes == 0) return 0;
   const Policy* forced = static_cast<const Policy*>(policy);
-  // A two-shot all-reduce larger than the staging half runs as consecutive segments; each segment is a
-  // complete collective on the alternating half, so the next segment's staging overlaps this one's tail.
+  // An all-reduce larger than the staging half runs as ONE kernel whose shards stream through per-rank windows of the
+  // staging half under back-pressure (layout.hpp: cyclic composed plan). Should the layout engine refuse (a forced policy
+  // that cannot cycle), it falls back to consecutive segments, each a complete collective on the alternating half.
   if (spec.type == CollectiveType::allReduce && bytes > h->ws.stagingTRSize) {
+    static const bool segmentsOnly = std::getenv("PURLIN_AR_SEGMENTS") != nullptr;
+    Plan whole;
+    if (!segmentsOnly && planFor(spec, h->ws, forced, whole, nullptr)) return launchPlan(h, whole, src, dst, s);
     const size_t seg = roundDown(h->ws.stagingTRSize, size_t(h->dev.world) * kAccessAlign);
     for (size_t off = 0; off < bytes; off += seg) {
       CollectiveSpec part = spec;

@@ -327,7 +327,10 @@ struct Sim {
           if ((s.flags & kFlagCyclic) && k >= s.slots) {
             const uint64_t need = flagValue(seq, k - s.slots);
             bool ok = true;
-            if (s.peer >= 0) ok = consumed(r, s.peer) >= need;
+            if (s.flags & kFlagDrainGather) {
+              if (s.peer != r) ok = gatherSignal(r, s.peer) >= need;
+              else for (int q = 0; q < W; ++q) { if (q != r && consumed(r, q) < need) ok = false; }
+            } else if (s.peer >= 0) ok = consumed(r, s.peer) >= need;
             else for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagDrainSelf)) continue; if (consumed(r, q) < need) ok = false; }
             if (!ok) return progressed;
           }

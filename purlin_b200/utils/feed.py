@@ -11,8 +11,10 @@ must not sit on the critical path:
     host            wait r(i-1), read it       wait r(i), read it
 
 ``depth`` device buffers rotate; a buffer is overwritten only after the step that read it has finished (event), a step
-starts only after its input has landed (event), and the host reads step i-1's result while step i runs.  Every step
-still performs its own host->device copy and its own device->host read; nothing is cached or skipped.
+starts only after its input has landed (event), and the host reads the result of step i - (depth - 1) while the later steps
+are already queued: with several ranks that wait for one another inside the fused kernels, a host that is late once
+(a timer thread, the interpreter lock) would otherwise stall every rank, every time. Every step still performs its own
+host->device copy and its own device->host read; nothing is cached or skipped.
 """
 from __future__ import annotations
 
@@ -22,7 +24,7 @@ import torch
 
 
 class HostFeed:
-    def __init__(self, shape, dtype: torch.dtype, device, depth: int = 2):
+    def __init__(self, shape, dtype: torch.dtype, device, depth: int = 4):
         if depth < 2:
             raise ValueError("overlap needs at least two device buffers")
         self.device = torch.device(device)
@@ -45,10 +47,11 @@ class HostFeed:
         """
         cur = torch.cuda.current_stream(self.device)
         out: List[float] = []
-        pending = None   # (slot, step index) whose result has not been read yet
+        pending = []     # (slot, step index) of the steps whose results have not been read yet, oldest first
+        lag = self.depth - 1   # results are read this many steps late; a result slot is read before it is reused
 
         def collect():
-            slot, idx = pending
+            slot, idx = pending.pop(0)
             self.done[slot].synchronize()
             v = float(self.results[slot][0])
             out.append(v)
@@ -70,9 +73,9 @@ class HostFeed:
             self.consumed[s].record(cur)
             self.results[s].copy_(metric.reshape(1).to(torch.float32), non_blocking=True)
             self.done[s].record(cur)
-            if pending is not None:
-                collect()                                              # step i-1's result, read while step i runs
-            pending = (s, i)
-        if pending is not None:
+            pending.append((s, i))
+            while len(pending) > lag:
+                collect()                                              # step i - lag's result, read while later steps run
+        while pending:
             collect()
         return out

@@ -103,3 +103,17 @@ def test_in_place_all_reduce_back_to_back(kw, world):
     calls = [(AR, n, None), (AG, n // world, None), (AR, n, None), (AR, n, None)]
     for seed in (51, 52, 53):
         _check(calls, world, seed=seed, dtype=4, policy=policy(**kw) if kw else None, in_place_ar=True)
+
+
+@pytest.mark.parametrize("world", [2, 3, 4, 8])
+@pytest.mark.parametrize("kw", [dict(), dict(chunkBytes=16384), dict(chunkBytes=4096, putBlocks=8, consumeBlocks=8, gatherBlocks=8),
+                                dict(arPath=1, memType=1, chunkBytes=8192)])
+def test_all_reduce_larger_than_staging_runs_as_one_plan(kw, world):
+    """Payloads beyond the staging half stream through per-rank windows under back-pressure: producers are released by the
+    reducers' gather signals, the seam slots by the gatherers. Back to back with other calls, under random schedules."""
+    staging = 256 << 10
+    n = (staging * 3 + 32 * world * 17) // (32 * world) * (32 * world)
+    small = 32 * world * 24
+    calls = [(AR, n, None), (AR, small, None), (AR, n, None), (AG, small // world, None), (AR, n + 32 * world, None), (RS, small // world, None)]
+    for seed in (61, 62, 63):
+        _check(calls, world, seed=seed, dtype=0, staging=staging, policy=policy(**kw) if kw else None, multicast=bool(kw.get("memType")))
