@@ -105,6 +105,7 @@ int purlin_vmm_multicast_create(PurlinVmmBlock* block, int* pid, int* fd);
 int purlin_vmm_multicast_join(PurlinVmmBlock* block, int pid, int fd);
 int purlin_vmm_multicast_bind(PurlinVmmBlock* block);
 uint64_t purlin_vmm_multicast_ptr(const PurlinVmmBlock* block);
+int purlin_vmm_exchange_done(void);   /* after the barrier that follows mapping: peers may no longer duplicate this process's descriptors */
 int purlin_vmm_detach(PurlinVmmBlock* block);
 int purlin_vmm_destroy(PurlinVmmBlock* block);
 

@@ -165,6 +165,7 @@ class VmmMemory {
       }
     }
     barrier_();
+    purlin_vmm_exchange_done();   // every rank has duplicated what it needs: close the descriptor-sharing window
     SymmetricAllocation a;
     for (int q = 0; q < world_; ++q) a.peers.push_back(reinterpret_cast<void*>(purlin_vmm_peer_ptr(block_, q)));
     a.multicast = reinterpret_cast<void*>(purlin_vmm_multicast_ptr(block_));

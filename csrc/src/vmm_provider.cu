@@ -19,6 +19,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <sys/prctl.h>
+
+#include <cstdlib>
 #include <sys/syscall.h>
 #include <unistd.h>
 
@@ -157,6 +159,13 @@ CUmulticastObjectProp multicastProp(int world, size_t bytes) {
 
 extern "C" {
 
+// Ends the window in which peers may duplicate this process's descriptors: back to the kernel's default (ancestors
+// only). Call on every rank after the barrier that follows mapping (and multicast binding).
+int purlin_vmm_exchange_done(void) {
+  if (std::getenv("PURLIN_VMM_NO_PTRACE_RELAX") == nullptr) prctl(PR_SET_PTRACER, 0, 0, 0, 0);
+  return 0;
+}
+
 // 1 when the device and the driver offer NVLS multicast objects, 0 when not, -1 on error
 int purlin_vmm_multicast_supported(int device) {
   const Driver& d = driver();
@@ -173,7 +182,10 @@ PurlinVmmBlock* purlin_vmm_create(int device, size_t bytes, int rank, int world)
   if (!d.ok) { purlin::setError("vmm provider: the driver lacks the virtual-memory entry points"); return nullptr; }
   if (world < 1 || world > purlin::kMaxRanks || rank < 0 || rank >= world || bytes == 0) { purlin::setError("vmm provider: invalid arguments"); return nullptr; }
   if (cudaSetDevice(device) != cudaSuccess || cudaFree(nullptr) != cudaSuccess) { purlin::setError("vmm provider: cannot use the device"); return nullptr; }
-  prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);   // lets the peers of this job duplicate the exported descriptors
+  // pidfd_getfd needs ptrace access to the exporting process. The relaxation lasts for the handle exchange only:
+  // purlin_vmm_exchange_done() restores the default once every rank has mapped what it needs (after the barrier).
+  // PURLIN_VMM_NO_PTRACE_RELAX=1 skips it altogether (for hosts where the ranks may read each other anyway).
+  if (world > 1 && std::getenv("PURLIN_VMM_NO_PTRACE_RELAX") == nullptr) prctl(PR_SET_PTRACER, PR_SET_PTRACER_ANY, 0, 0, 0);
   auto* b = new PurlinVmmBlock;
   b->device = device; b->rank = rank; b->world = world;
   b->peers.resize(size_t(world));

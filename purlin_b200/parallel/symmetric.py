@@ -179,6 +179,7 @@ def _vmm_provider(nbytes: int, device: torch.device, group):
 
     def give_up(what):
         err = _native.last_error(lib)
+        lib.purlin_vmm_exchange_done()
         if mapping.block:
             lib.purlin_vmm_destroy(C.c_void_p(mapping.block))
             mapping.block = None
@@ -204,6 +205,7 @@ def _vmm_provider(nbytes: int, device: torch.device, group):
             if not all(everyone(ok)):
                 give_up("binding the multicast object failed on some rank")
     dist.barrier(group)
+    lib.purlin_vmm_exchange_done()   # every rank has duplicated what it needs: close the descriptor-sharing window
     peer_ptrs = [int(lib.purlin_vmm_peer_ptr(C.c_void_p(block), q)) for q in range(world)]
     mc = int(lib.purlin_vmm_multicast_ptr(C.c_void_p(block)))
     return mapping, mapping, peer_ptrs, mc
