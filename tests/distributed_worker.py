@@ -116,6 +116,16 @@ def main():
     for n in (32 * W, 8 << 10, 64 << 10, 512 << 10, 4 << 20):
         for coll, cname in ((AR, "AR"), (AG, "AG"), (RS, "RS"), (A2A, "A2A")):
             case(f"{cname} default {n}", coll, nbytes=n, dtype=0, reps=1)
+    # a CTA budget of 64 (the reference's cap on a collective): the same calls must stay exact with the smaller grids
+    old_budget = purlin.set_max_ctas(64)
+    for n in (64 << 10, 4 << 20):
+        for coll, cname in ((AR, "AR"), (AG, "AG"), (RS, "RS"), (A2A, "A2A")):
+            case(f"{cname} budget 64 CTAs {n}", coll, nbytes=n, dtype=0, reps=1)
+    purlin.set_max_ctas(old_budget)
+    # an all-reduce beyond the staging size is one kernel; here with the reduction done by the switch
+    if mc and not subset:
+        case("AR cyclic nvls", AR, nbytes=staging * 2 + W * 32 * 8, dtype=0,
+             pol=policy(arPath=1, memType=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=1 << 20))
     case("AR default graph", AR, nbytes=64 << 10, dtype=0, reps=1, graph=True)
     case("AR default graph large", AR, nbytes=2 << 20, dtype=0, reps=1, graph=True)
     # variable-length

@@ -48,6 +48,11 @@ def test_route_noalloc_matches_context_route_twice():
         rc = fn(logits.data_ptr(), tokens, experts, topk, 1, idx.data_ptr(), w.data_ptr(), slot.data_ptr(), stream)
         assert rc == 0, _native.last_error(lib)
         torch.cuda.synchronize()
+        # and against plain PyTorch: softmax, top-k, renormalised weights (ids as sets per token: equal logits may tie)
+        tw, ti = torch.topk(torch.softmax(logits, dim=-1), topk, dim=-1)
+        tw = tw / tw.sum(-1, keepdim=True)
+        assert torch.equal(torch.sort(idx.long(), dim=-1).values, torch.sort(ti, dim=-1).values), f"call {call}: ids differ from torch.topk"
+        assert torch.allclose(torch.sort(w, dim=-1).values, torch.sort(tw, dim=-1).values, atol=1e-5, rtol=1e-4)
         assert torch.equal(idx, ref_idx), f"call {call}: expert ids differ"
         assert torch.equal(w, ref_w), f"call {call}: gate weights differ"
         ok, counts = _slots_are_a_numbering(idx, slot, experts)
