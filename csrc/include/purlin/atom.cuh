@@ -10,11 +10,13 @@
 //
 // Parity: the Atom contract of csrc/include/purlin/atom.cuh:9-12 and the sm_100
 // datapath of cortex.cuh:9-59 / ligament.cuh:20-152 in the reference. This is a
-// Blackwell-only implementation: copies move 32 bytes per access (ld/st.global.v8);
-// reductions load 32 bytes per peer per access when the plan asks for it and the
-// buffers are 32-byte aligned (16 bytes otherwise, and 16 on the NVLS path, whose
-// multimem.ld_reduce is at most 128 bits wide); arithmetic is packed f32x2; the number
-// of accesses in flight per thread is a knob chosen by the tuning policy.
+// Blackwell-only implementation: copies move 32 bytes per access (ld/st.global.v8).
+// Reductions load 16 bytes per peer per access: a 32-byte form was built and measured
+// on B200 over NVLink (2 GPUs, reduce-scatter of 32 MiB / 256 MiB: 83 / 507 us against
+// 64 / 331 us) and, compiled into the same kernel, pushed every reduce instantiation
+// into register spills, so it was taken out again; multimem.ld_reduce is 128 bits wide
+// at most in any case. Arithmetic is packed f32x2; the number of accesses in flight per
+// thread is a knob chosen by the tuning policy.
 #pragma once
 #include "math.cuh"
 #include "signal.cuh"
@@ -124,25 +126,13 @@ struct AtomSm100 {
   // One CTA reduces `bytes` (a multiple of 16) of every rank's slice. `mmDepth` = multimem loads in flight per
   // thread on the NVLS path (1, 2, 4 or 8).
   template <DType T, ReduceOp Op>
-  static PURLIN_D void reduce(const ReduceArgs& a, int mmDepth = MmDepth, bool wide = false) {
+  static PURLIN_D void reduce(const ReduceArgs& a, int mmDepth = MmDepth) {
     if constexpr (MultimemReducible<T, Op>::value) {
       if (a.mcSrc != nullptr) {
         if (mmDepth >= 8) reduceMultimem<T, Op, 8>(a);
         else if (mmDepth >= 4) reduceMultimem<T, Op, 4>(a);
         else if (mmDepth >= 2) reduceMultimem<T, Op, 2>(a);
         else reduceMultimem<T, Op, 1>(a);
-        return;
-      }
-    }
-    // 32-byte loads when every pointer and the length allow it (the plan asks for them): twice the bytes in flight per
-    // thread and half the instructions of the 16-byte form
-    if (wide && a.world <= 8 && a.bytes % 32 == 0 && ((reinterpret_cast<uintptr_t>(a.dst) | reinterpret_cast<uintptr_t>(a.seam)) & 31u) == 0 && a.mcSeam == nullptr) {
-      bool aligned = true;
-      for (int b = 0; b < a.world; ++b) aligned = aligned && (reinterpret_cast<uintptr_t>(a.srcs[b]) & 31u) == 0;
-      if (aligned) {
-        if (a.world <= 2) reduceUnicastWide<T, Op, 2>(a);
-        else if (a.world <= 4) reduceUnicastWide<T, Op, 4>(a);
-        else reduceUnicastWide<T, Op, 8>(a);
         return;
       }
     }
@@ -165,42 +155,6 @@ struct AtomSm100 {
       for (int d = 0; d < D; ++d) emit(a, (i + size_t(d) * nt) * 16, v[d]);
     }
     for (; i < n; i += nt) emit(a, i * 16, multimemLdReduce<T, Op>(a.mcSrc + i * 16));
-  }
-
-  // The same reduction on 32-byte vectors (ld/st.global.v8): U = 8 / WB vectors of every peer in flight per thread,
-  // ascending rank order, fp32 accumulation. Callers guarantee 32-byte alignment of every pointer and of the length.
-  template <DType T, ReduceOp Op, int WB>
-  static PURLIN_D void reduceUnicastWide(const ReduceArgs& a) {
-    constexpr int U = 8 / WB;
-    const int tid = threadIdx.x, nt = blockDim.x;
-    const size_t n = a.bytes / 32;
-    for (size_t i0 = tid; i0 < n; i0 += size_t(U) * nt) {
-      Vec32 v[U][WB];
-#pragma unroll
-      for (int u = 0; u < U; ++u)
-#pragma unroll
-        for (int b = 0; b < WB; ++b)
-          if (b < a.world && i0 + size_t(u) * nt < n) v[u][b] = ld32(a.srcs[b] + (i0 + size_t(u) * nt) * 32);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (i0 + size_t(u) * nt >= n) break;
-        Vec32 out;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          Acc<T> acc;
-#pragma unroll
-          for (int e = 0; e < ElemTraits<T>::perWord; ++e) acc.v[e] = identity<Op>();
-#pragma unroll
-          for (int b = 0; b < WB; ++b)
-            if (b < a.world) accumulate<T, Op>(acc, unpack<T>(uint64_t(v[u][b].x[2 * w]) | (uint64_t(v[u][b].x[2 * w + 1]) << 32)));
-          const uint64_t r = pack<T>(acc);
-          out.x[2 * w] = uint32_t(r); out.x[2 * w + 1] = uint32_t(r >> 32);
-        }
-        const size_t off = (i0 + size_t(u) * nt) * 32;
-        if (a.dst) st32(a.dst + off, out);
-        if (a.seam) st32(a.seam + off, out);
-      }
-    }
   }
 
   // Worlds of at most 8 ranks: every peer's copy of U = 8 / WB consecutive vectors is requested before any is

@@ -115,9 +115,7 @@ struct Policy {
   uint64_t chunkBytes = 0;      // 0: one flag per stream
   uint64_t perStreamThreshold = 128ull << 10;
   int32_t maxCtas = 0;          // > 0: the plan may use at most this many CTAs (the collective shares the GPU with other work)
-  int32_t wideReduce = 0;       // 1: unicast reductions move 32 bytes per access where alignment allows. Measured on B200
-                                // over NVLink (2 GPUs, reduce-scatter 32 MiB / 256 MiB): 83 / 507 us against 64 / 331 us
-                                // for the 16-byte form, so the default stays 16 bytes
+  int32_t reserved = 0;
 };
 
 // Shrinks the CTA counts of a policy so that a plan built from it fits `budget` CTAs, given that the plan built from the
@@ -249,7 +247,6 @@ inline bool buildPlan(const CollectiveSpec& spec, const Policy& pol, const Works
   plan.threads = pol.threads;
   plan.mmDepth = pol.mmDepth;
   plan.unroll = pol.unroll;
-  plan.wideReduce = pol.wideReduce;
   plan.stageDepth = std::min(std::max(pol.stageDepth, 0), bulk::kPlanMaxDepth);
   if (plan.stageDepth == 1) plan.stageDepth = 2;   // a ring needs a tile in flight and a tile being stored
   plan.smemBytes = (plan.stageDepth > 0 && pol.regime == int32_t(Regime::throughput)) ? size_t(plan.stageDepth) * bulk::kPlanTileBytes + 256 : 0;

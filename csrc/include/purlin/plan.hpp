@@ -89,7 +89,7 @@ struct PlanT {
   int32_t mmDepth;        // multimem loads in flight per thread
   int32_t unroll;         // vector accesses in flight per thread in the plain datapath
   int32_t stageDepth;     // stages of the bulk-async ring (0: plain vector datapath)
-  int32_t wideReduce;     // 1: unicast reductions use 32-byte loads and stores where alignment allows
+  int32_t reserved;
   uint64_t smemBytes;
   uint64_t payloadBytes;  // logical bytes for reports
   Step steps[N];
@@ -103,7 +103,7 @@ inline void compactPlan(const Plan& in, PlanCompact& out) {
   out.collective = in.collective; out.regime = in.regime; out.consumeOp = in.consumeOp; out.reduceOp = in.reduceOp;
   out.dtype = in.dtype; out.deterministic = in.deterministic; out.blocks = in.blocks; out.threads = in.threads;
   out.nSteps = in.nSteps; out.varLenArrival = in.varLenArrival; out.mmDepth = in.mmDepth; out.unroll = in.unroll;
-  out.stageDepth = in.stageDepth; out.wideReduce = in.wideReduce; out.smemBytes = in.smemBytes; out.payloadBytes = in.payloadBytes;
+  out.stageDepth = in.stageDepth; out.reserved = in.reserved; out.smemBytes = in.smemBytes; out.payloadBytes = in.payloadBytes;
   for (int i = 0; i < kCompactSteps; ++i) out.steps[i] = in.steps[i];
 }
 

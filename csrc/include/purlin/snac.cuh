@@ -38,7 +38,6 @@ struct Frame {
   unsigned char* dst;
   int unroll;
   int mmDepth;
-  bool wideReduce;
   int bulkDepth;            // > 0: copy roles stream through the bulk-async ring in `smem`
   unsigned char* smem;
 };
@@ -235,7 +234,7 @@ PURLIN_D bool reduce(const Context& ctx, const Step& s, int si, const Frame& f, 
       if (s.flags & kFlagMulticastOut) a.mcSeam = ctx.mcStagingTR + so;
       else a.seam = ctx.stagingTR[ctx.rank] + so;
     }
-    if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth, f.wideReduce);
+    if (sp.bytes) Atom::template reduce<T, Op>(a, f.mmDepth);
     if (s.flags & (kFlagNotifyGather | kFlagCyclic)) {
       if (s.flags & kFlagMulticastOut) __threadfence_system();
       if (ctaLastArrival(ctx.counters + s.counterBase + (k % kMaxChunks), n) && int(threadIdx.x) < ctx.world) {
@@ -372,7 +371,6 @@ PURLIN_D void run(const Context& ctx, const PlanType& plan, const unsigned char*
   f.dst = dst;
   f.unroll = plan.unroll;
   f.mmDepth = plan.mmDepth;
-  f.wideReduce = plan.wideReduce != 0;
   f.bulkDepth = plan.regime == int32_t(Regime::throughput) ? plan.stageDepth : 0;
   f.smem = dynSmem;
   // A context that failed stays quiet until the host clears it. The status word is requested here and looked at after

@@ -653,7 +653,7 @@ int smCount() {
 // Environment switches, read once per process (they select code paths for experiments, not per-call behaviour).
 struct Switches {
   bool singleCta, oneAcc;
-  int agCommWarps, agPushParts;
+  int agCommWarps, agPushParts, rsAccs;
 };
 const Switches& switches() {
   static const Switches sw = [] {
@@ -665,6 +665,7 @@ const Switches& switches() {
     // instruction of its SM, the epilogue's included.
     v.agCommWarps = std::min(std::max(num("PURLIN_AG_COMM_WARPS", 1), 1), kCommWarps);
     v.agPushParts = std::min(std::max(num("PURLIN_AG_PUSH_PARTS", 8), 1), 64);
+    v.rsAccs = num("PURLIN_RS_ACCS", 0);
     return v;
   }();
   return sw;
@@ -695,7 +696,7 @@ int ctasFor(int M, int rowsPerRank) {
 
 struct Shape { int ctas, accs; };
 
-bool fillShape(Params& p, Shape& sh, int M, int N, int K, int epilogue, int bn, int rowsPerRank) {
+bool fillShape(Params& p, Shape& sh, int M, int N, int K, int epilogue, int bn, int rowsPerRank, int accsWanted = 0) {
   if (M <= 0 || N <= 0 || K <= 0) { setError("GEMM dimensions must be positive"); return false; }
   if (K % 8 || N % 8) { setError("N and K must be multiples of 8"); return false; }
   const int ctas = ctasFor(M, rowsPerRank);
@@ -705,7 +706,7 @@ bool fillShape(Params& p, Shape& sh, int M, int N, int K, int epilogue, int bn, 
   if (ctas == 2 && (bn / 2) % 8) { setError("a CTA pair needs a tile width that is a multiple of 16"); return false; }
   // two accumulators per tile (512 rows) whenever the rows allow it: a third fewer operand bytes per flop, and MMAs
   // that alternate between two accumulators while sharing B run faster than a chain into one accumulator
-  const int accs = (ctas == 2 && !switches().oneAcc && 2 * bn <= kTmemCols && rowsPerRank % (4 * kBM) == 0 && M % (4 * kBM) == 0) ? 2 : 1;
+  const int accs = (ctas == 2 && !switches().oneAcc && accsWanted != 1 && 2 * bn <= kTmemCols && rowsPerRank % (4 * kBM) == 0 && M % (4 * kBM) == 0) ? 2 : 1;
   sh.ctas = ctas; sh.accs = accs;
   const int tileRows = kBM * ctas * accs;
   p.tilesM = (M + tileRows - 1) / tileRows; p.tilesN = (N + bn - 1) / bn;
@@ -923,7 +924,7 @@ int purlin_tp_gemm_rs(PurlinTpContext* c, const void* A, const void* W, void* ou
   if (M > c->M || N > c->nRs || M % (c->world * kBM)) { setError("GEMM reduce-scatter shape exceeds the workspace or rows per rank are not a multiple of 128"); return 1; }
   Params p{};
   Shape sh{};
-  if (!fillShape(p, sh, M, N, K, kEpiStore, 0, M / c->world)) return 1;
+  if (!fillShape(p, sh, M, N, K, kEpiStore, 0, M / c->world, switches().rsAccs)) return 1;
   unsigned char* lb = static_cast<unsigned char*>(c->local);
   p.rank = c->rank; p.world = c->world; p.blocksPerRank = M / c->world / (kBM * sh.ctas * sh.accs);
   p.epoch = reinterpret_cast<uint64_t*>(lb + 128); p.exitCounter = reinterpret_cast<uint32_t*>(lb + 192);

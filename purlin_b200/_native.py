@@ -37,7 +37,7 @@ class Plan(C.Structure):
         ("collective", C.c_int32), ("regime", C.c_int32), ("consumeOp", C.c_int32), ("reduceOp", C.c_int32),
         ("dtype", C.c_int32), ("deterministic", C.c_int32), ("blocks", C.c_int32), ("threads", C.c_int32),
         ("nSteps", C.c_int32), ("varLenArrival", C.c_int32), ("mmDepth", C.c_int32), ("unroll", C.c_int32),
-        ("stageDepth", C.c_int32), ("wideReduce", C.c_int32),
+        ("stageDepth", C.c_int32), ("reserved", C.c_int32),
         ("smemBytes", C.c_uint64), ("payloadBytes", C.c_uint64),
         ("steps", Step * K_MAX_STEPS),
     ]
@@ -53,7 +53,7 @@ class Policy(C.Structure):
         ("mmDepth", C.c_int32), ("unroll", C.c_int32), ("stageDepth", C.c_int32), ("arPath", C.c_int32),
         ("lrMulticast", C.c_int32), ("weighted", C.c_int32),
         ("chunkBytes", C.c_uint64), ("perStreamThreshold", C.c_uint64),
-        ("maxCtas", C.c_int32), ("wideReduce", C.c_int32),
+        ("maxCtas", C.c_int32), ("reserved", C.c_int32),
     ]
 
     def as_dict(self):
@@ -62,7 +62,7 @@ class Policy(C.Structure):
     @classmethod
     def from_dict(cls, d):
         """A policy from a stored table entry. Fields that are newer than the entry keep the engine's defaults
-        (16-byte reductions, no CTA budget); fields the engine no longer has are ignored."""
+        (no CTA budget); fields the engine no longer has are ignored."""
         p = cls()
         names = {n for n, _ in cls._fields_}
         for k, v in d.items():
