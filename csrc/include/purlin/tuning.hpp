@@ -44,10 +44,17 @@ class TuningTable {
     std::stable_sort(entries_.begin(), entries_.end(), [](const TuningEntry& a, const TuningEntry& b) { return a.maxBytes < b.maxBytes; });
   }
   size_t size() const { return entries_.size(); }
+  // The band that holds `bytes`; a payload beyond the largest measured band takes that band's policy (what was measured
+  // at 256 MiB is a better guess for 1 GiB than the built-in starting point).
   bool lookup(CollectiveType c, int world, uint64_t bytes, Policy& out) const {
     std::lock_guard<std::mutex> g(mu_);
-    for (const TuningEntry& e : entries_)
-      if (e.collective == int32_t(c) && e.world == world && bytes <= e.maxBytes) { out = e.policy; return true; }
+    const TuningEntry* largest = nullptr;
+    for (const TuningEntry& e : entries_) {
+      if (e.collective != int32_t(c) || e.world != world) continue;
+      if (bytes <= e.maxBytes) { out = e.policy; return true; }
+      largest = &e;     // entries are sorted by band
+    }
+    if (largest) { out = largest->policy; return true; }
     return false;
   }
  private:

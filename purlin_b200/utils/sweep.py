@@ -369,10 +369,10 @@ def main():
                         print(bench.csv_row(coll, "purlin_b200:" + tag, world, total, args.dtype, t, 0.0 if oks else 100.0), flush=True)
                 del stt
             if ref_mod is not None and not args.tune:
-                rstream = torch.cuda.current_stream().cuda_stream
                 rout = torch.empty_like(out)
 
                 def ref_call():
+                    rstream = torch.cuda.current_stream().cuda_stream     # at call time: under graph capture this is the capturing stream
                     if coll == "ar":
                         ref_mod.all_reduce(x, rout, ref_h, rstream)
                     elif coll == "ag":
