@@ -152,6 +152,25 @@ def bench_moe(rank, world, dev, args, unfused=True):
     if world > 1:
         dist.all_reduce(tt, op=dist.ReduceOp.MAX)
     d_us, c_us = float(tt[0]), float(tt[1])
+    # optional: the same split for other CTA counts of the pushing roles ("senders:pushers,...")
+    for pair in [c for c in getattr(args, "moe_sweep", "").split(",") if c]:
+        os.environ["PURLIN_MOE_SENDERS"], os.environ["PURLIN_MOE_PUSHERS"] = pair.split(":")
+        for _ in range(3):
+            both()
+        sd, sc = 0.0, 0.0
+        for _ in range(args.runs):
+            ev[0].record(); ep.dispatch(x); ev[1].record(); ep.combine(T, y); ev[2].record()
+            ev[2].synchronize()
+            sd += ev[0].elapsed_time(ev[1]) * 1e3
+            sc += ev[1].elapsed_time(ev[2]) * 1e3
+        st = torch.tensor([sd / args.runs, sc / args.runs], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(st, op=dist.ReduceOp.MAX)
+        emit(rank, path="MoE CTA sweep", world=world, senders=int(os.environ["PURLIN_MOE_SENDERS"]), pushers=int(os.environ["PURLIN_MOE_PUSHERS"]),
+             dispatch_us=round(float(st[0]), 1), combine_us=round(float(st[1]), 1))
+    if getattr(args, "moe_sweep", ""):
+        os.environ.pop("PURLIN_MOE_SENDERS", None)
+        os.environ.pop("PURLIN_MOE_PUSHERS", None)
     emit(rank, path="MoE dispatch (+permute)", world=world, tokens_per_rank=T, hidden=H, experts=E, topk=K, us=round(d_us, 1),
          roofline_us=round(roof_us, 1), roofline_frac=round(roof_us / d_us, 3), link_GB=round(link_bytes / 1e9, 3),
          achieved_link_GBps=round(link_bytes / d_us / 1e3, 1), per_pair_link_GB=round(pair_bytes / 1e9, 3),
@@ -160,6 +179,22 @@ def bench_moe(rank, world, dev, args, unfused=True):
          roofline_frac=round(roof_us / c_us, 3), achieved_link_GBps=round(link_bytes / c_us / 1e3, 1),
          frac_of_per_pair_roofline=round(pair_roof_us / c_us, 3))
     emit(rank, path="MoE dispatch+combine pair", world=world, us=round(t_pair.us, 1), roofline_frac=round(2 * roof_us / t_pair.us, 3))
+    if os.environ.get("PURLIN_MOE_TIMING"):
+        # device-side phase times of one pair (max over ranks): where the senders / pushers and the receivers / finishers end
+        ep.timing()
+        if world > 1:
+            dist.barrier()
+        both()
+        ph = ep.timing()
+        flat = [ph["dispatch"]["first_sender"], ph["dispatch"]["last_sender"], ph["dispatch"]["last_receiver"],
+                ph["combine"]["first_pusher"], ph["combine"]["last_pusher"], ph["combine"]["last_finisher"]]
+        pt = torch.tensor(flat, device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(pt, op=dist.ReduceOp.MAX)
+        names = ("dispatch_first_sender_us", "dispatch_last_sender_us", "dispatch_last_receiver_us",
+                 "combine_first_pusher_us", "combine_last_pusher_us", "combine_last_finisher_us")
+        emit(rank, path="MoE phases (device clock, from each kernel's first CTA)", world=world,
+             **{n: round(float(v), 1) for n, v in zip(names, pt.tolist())})
     # unfused baseline: sort rows by destination, NCCL all-to-all of the counts and of the rows, and back, then a weighted sum
     if world > 1 and unfused:
         flat = idx.flatten().long()
@@ -190,6 +225,8 @@ def main():
     ap.add_argument("--what", default="tp,moe")
     ap.add_argument("--runs", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--moe-sweep", default="", help='extra MoE rows for other CTA counts: "senders:pushers,senders:pushers"')
+    ap.add_argument("--no-unfused", action="store_true", help="skip the NCCL + torch compositions")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -201,7 +238,7 @@ def main():
     if "tp" in args.what:
         bench_tp(rank, world, dev, args)
     if "moe" in args.what:
-        bench_moe(rank, world, dev, args)
+        bench_moe(rank, world, dev, args, unfused=not args.no_unfused)
     if world > 1:
         dist.destroy_process_group()
 

@@ -527,6 +527,15 @@ inline bool buildLatencyPlan(const CollectiveSpec& spec, const Policy& pol, cons
   const int n = std::max(pol.lrBlocks, 1);
   auto one = [&](Step s) { s.chunkBytes = s.bytes; s.chunks = 1; s.slots = 1; s.blockBegin = 0; s.blockCount = n; return b.add(s); };
   const bool mc = pol.lrMulticast && spec.multicastAvailable && spec.mode == ReductionMode::nonDeterministic;
+  // Equal slices at q * bytes from a common base (every fixed-size form): the packets of all peers are fetched by ONE step
+  // whose (peer, word) pairs are spread over the threads, so a rank polls its W - 1 peers at the same time instead of one
+  // after the other with a CTA barrier between them (one memory round trip instead of W - 1).
+  auto equalSlices = [&](const size_t* off, const size_t* len) {
+    if (plan.varLenArrival || W < 2 || len[r] == 0 || off[r] < size_t(r) * len[r]) return false;
+    const size_t base = off[r] - size_t(r) * len[r];
+    for (int q = 0; q < W; ++q) if (len[q] != len[r] || off[q] != base + size_t(q) * len[r]) return false;
+    return true;
+  };
 
   if (isPacked(spec.in) && !composed) {
     // all-gather family and one-shot all-reduce: the same words go to every peer
@@ -547,11 +556,16 @@ inline bool buildLatencyPlan(const CollectiveSpec& spec, const Policy& pol, cons
       Step l{}; l.role = kRoleLocal; l.peer = r; l.srcOff = isScattered(spec.in) ? pt.sendOff[r] : 0; l.dstOff = pt.recvOff[r]; l.bytes = pt.recv[r];
       if (!one(l)) return false;
     }
-    for (int k = 1; k < W; ++k) {
-      const int q = (r + k) % W;
-      if (pt.recv[q] > cap) { err = "payload exceeds the packet slot"; return false; }
-      Step g{}; g.role = kRolePacketGet; g.peer = q; g.srcOff = 0; g.dstOff = pt.recvOff[q]; g.bytes = pt.recv[q];
+    for (int k = 1; k < W; ++k) if (pt.recv[(r + k) % W] > cap) { err = "payload exceeds the packet slot"; return false; }
+    if (equalSlices(pt.recvOff, pt.recv)) {
+      Step g{}; g.role = kRolePacketGet; g.peer = -1; g.srcOff = 0; g.dstOff = pt.recvOff[r] - size_t(r) * pt.recv[r]; g.bytes = pt.recv[r]; g.seamOff = uint64_t(r);
       if (!one(g)) return false;
+    } else {
+      for (int k = 1; k < W; ++k) {
+        const int q = (r + k) % W;
+        Step g{}; g.role = kRolePacketGet; g.peer = q; g.srcOff = 0; g.dstOff = pt.recvOff[q]; g.bytes = pt.recv[q];
+        if (!one(g)) return false;
+      }
     }
   } else {
     Step red{}; red.role = kRolePacketReduce; red.peer = -1;
@@ -560,7 +574,11 @@ inline bool buildLatencyPlan(const CollectiveSpec& spec, const Policy& pol, cons
     red.flags |= kFlagToDst;
     if (composed) { red.flags |= kFlagPublish; if (mc) red.flags |= kFlagMulticastOut; }
     if (!one(red)) return false;
-    if (composed) {
+    if (composed && equalSlices(pt.sendOff, pt.send)) {
+      Step g{}; g.role = kRolePacketGet; g.peer = -1; g.srcOff = 0; g.dstOff = pt.sendOff[r] - size_t(r) * pt.send[r]; g.bytes = pt.send[r]; g.seamOff = uint64_t(r);
+      g.flags |= kFlagResultHalf;
+      if (!one(g)) return false;
+    } else if (composed) {
       for (int k = 1; k < W; ++k) {
         const int q = (r + k) % W;
         Step g{}; g.role = kRolePacketGet; g.peer = q; g.srcOff = 0; g.dstOff = pt.sendOff[q]; g.bytes = pt.send[q];

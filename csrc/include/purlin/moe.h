@@ -26,6 +26,10 @@ PurlinMoeContext* purlin_moe_create(int rank, int world, const uint64_t* peerPtr
 int purlin_moe_destroy(PurlinMoeContext* ctx, void* stream);
 int purlin_moe_status(PurlinMoeContext* ctx, uint32_t* out4, void* stream);
 int purlin_moe_clear_status(PurlinMoeContext* ctx, void* stream);
+/* Diagnostics (contexts created with PURLIN_MOE_TIMING=1): nanoseconds from the first CTA's start to {last sender end, last
+ * receiver end, first sender end, 0} of the dispatches and {last pusher end, last finisher end, first pusher end, 0} of the
+ * combines since the previous call of this function. Synchronises the stream. */
+int purlin_moe_timing(PurlinMoeContext* ctx, uint64_t* out8, void* stream);
 void* purlin_moe_recv_buffer(PurlinMoeContext* ctx);   /* [capacityRows, hidden] bf16, expert-major after dispatch */
 void* purlin_moe_out_buffer(PurlinMoeContext* ctx);    /* [capacityRows, hidden] bf16, written by the experts, read by combine */
 

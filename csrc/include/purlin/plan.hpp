@@ -36,7 +36,8 @@ enum Role : int32_t {
   kRoleReduce = 3,    // wait signals[rank][*]; reduce every rank's staging -> dst and/or seam
   kRoleGather = 4,    // composed tail: wait gatherSignals[rank][peer]; peer seam -> user dst
   kRolePacketPut = 5, // latency: user src words -> packets in peer's slot (-1: every peer)
-  kRolePacketGet = 6, // latency: packets from `peer` in own slot -> user dst
+  kRolePacketGet = 6, // latency: packets from `peer` in own slot -> user dst. peer -1: from every peer q, `bytes` each, to
+                      // dstOff + q * bytes (equal slices; seamOff holds this rank's index, whose slice is not touched)
   kRolePacketReduce = 7,  // latency: reduce own words with every peer's packets -> dst (+ publish)
 };
 

@@ -50,9 +50,9 @@ inline bool within(size_t off, size_t len, size_t limit) { return off <= limit &
 // Every byte of the user's output must be written by exactly one step: the ranges the steps write to `dst` have to
 // tile [0, dstBytes) with neither a gap (stale output) nor an overlap (two writers racing). An in-place call may leave
 // the rank's own slice untouched, so only overlaps are errors there.
-inline std::string checkCoverage(const Plan& plan, const PlanExtents& ext) {
+inline std::string checkCoverage(const Plan& plan, int world, const PlanExtents& ext) {
   struct Range { size_t begin, end; int step; };
-  Range ranges[kMaxSteps];
+  Range ranges[kMaxSteps + kMaxRanks];
   int n = 0;
   for (int i = 0; i < plan.nSteps; ++i) {
     const Step& s = plan.steps[i];
@@ -62,7 +62,13 @@ inline std::string checkCoverage(const Plan& plan, const PlanExtents& ext) {
       case kRoleReduce: writes = (s.flags & kFlagToDst) != 0; break;
       default: break;
     }
-    if (writes && s.bytes) ranges[n++] = Range{size_t(s.dstOff), size_t(s.dstOff + s.bytes), i};
+    if (writes && s.bytes && s.role == kRolePacketGet && s.peer < 0) {
+      // packets of every peer in one step: slice q lands at dstOff + q * bytes, this rank's own slice is left alone
+      for (int q = 0; q < world && n < kMaxSteps + kMaxRanks; ++q)
+        if (uint64_t(q) != s.seamOff) ranges[n++] = Range{size_t(s.dstOff + uint64_t(q) * s.bytes), size_t(s.dstOff + uint64_t(q + 1) * s.bytes), i};
+      continue;
+    }
+    if (writes && s.bytes && n < kMaxSteps + kMaxRanks) ranges[n++] = Range{size_t(s.dstOff), size_t(s.dstOff + s.bytes), i};
   }
   for (int a = 1; a < n; ++a)                       // insertion sort: at most kMaxSteps entries
     for (int b = a; b > 0 && ranges[b].begin < ranges[b - 1].begin; --b) { const Range t = ranges[b]; ranges[b] = ranges[b - 1]; ranges[b - 1] = t; }
@@ -117,7 +123,9 @@ inline std::string checkPlan(const Plan& plan, int world, const WorkspaceLayout&
           if (!detail::within(s.dstOff * 2, words * 16, slotBytes)) return bad(i, "packet slot (put)", s.dstOff * 2, words * 16, slotBytes);
           break;
         case kRolePacketGet:
-          if (!detail::within(s.dstOff, s.bytes, ext.dstBytes)) return bad(i, "destination", s.dstOff, s.bytes, ext.dstBytes);
+          if (s.peer < 0 && s.seamOff >= uint64_t(world)) return bad(i, "own slice index of an all-peers get", s.seamOff, 1, size_t(world));
+          if (!detail::within(s.dstOff, s.peer < 0 ? s.bytes * size_t(world) : s.bytes, ext.dstBytes))
+            return bad(i, "destination", s.dstOff, s.peer < 0 ? s.bytes * size_t(world) : s.bytes, ext.dstBytes);
           if (!detail::within(s.srcOff * 2, words * 16, (s.flags & kFlagResultHalf) ? ws.packetStride / 2 : slotBytes))
             return bad(i, "packet slot (get)", s.srcOff * 2, words * 16, slotBytes);
           break;
@@ -171,7 +179,7 @@ inline std::string checkPlan(const Plan& plan, int world, const WorkspaceLayout&
         return buf;
     }
   }
-  return checkCoverage(plan, ext);
+  return checkCoverage(plan, world, ext);
 }
 
 }  // namespace purlin

@@ -296,8 +296,23 @@ PURLIN_D bool packetGet(const Context& ctx, const Step& s, int si, const Frame& 
   const size_t words = s.bytes / 8, stride = size_t(s.blockCount) * blockDim.x;
   uint64_t* dst = reinterpret_cast<uint64_t*>(f.dst + s.dstOff);
   const uint64_t flag = flagValue(f.seq, 0);
-  const Packet* slot = slotOf(ctx, ctx.rank, s.peer, f.half, (s.flags & kFlagResultHalf) != 0) + s.srcOff / 8;
   bool ok = true;
+  if (s.peer < 0) {
+    // Every peer's packets in one step: (peer, word) pairs are spread over the threads, so the W - 1 peers are polled at
+    // the same time and the step ends with one barrier (the reference polls its peers from separate warps for the same
+    // reason, csrc/include/purlin/snac.cuh:1230-1262).
+    const size_t pairs = words * size_t(ctx.world - 1);
+    const size_t first = s.srcOff / 8;
+    for (size_t idx = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; idx < pairs && ok; idx += stride) {
+      const size_t i = idx % words;
+      const int q = (ctx.rank + 1 + int(idx / words)) % ctx.world;
+      uint64_t v;
+      ok = pkt::read(ctx, slotOf(ctx, ctx.rank, q, f.half, (s.flags & kFlagResultHalf) != 0) + first + i, flag, v, kStatusTimeoutPacket, si, q);
+      if (ok) reinterpret_cast<uint64_t*>(f.dst + s.dstOff + size_t(q) * s.bytes)[i] = v;
+    }
+    return ok;
+  }
+  const Packet* slot = slotOf(ctx, ctx.rank, s.peer, f.half, (s.flags & kFlagResultHalf) != 0) + s.srcOff / 8;
   for (size_t i = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; i < words && ok; i += stride) {
     uint64_t v;
     ok = pkt::read(ctx, slot + i, flag, v, kStatusTimeoutPacket, si, s.peer);
@@ -319,10 +334,24 @@ PURLIN_D bool packetReduce(const Context& ctx, const Step& s, int si, const Fram
 #pragma unroll
     for (int e = 0; e < ElemTraits<T>::perWord; ++e) acc.v[e] = identity<Op>();
     const uint64_t mine = own[i];
-    for (int q = 0; q < ctx.world && ok; ++q) {    // ascending rank order: bit-reproducible
-      uint64_t w = mine;
-      if (q != ctx.rank) ok = pkt::read(ctx, slotOf(ctx, ctx.rank, q, f.half, false) + first + i, flag, w, kStatusTimeoutPacket, si, q);
-      accumulate<T, Op>(acc, unpack<T>(w));
+    // ascending rank order (bit-reproducible); the packets of four ranks are requested before any is looked at, so a
+    // word costs a quarter of the memory round trips of a poll per rank
+    for (int q0 = 0; q0 < ctx.world && ok; q0 += 4) {
+      Packet v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (q0 + u < ctx.world && q0 + u != ctx.rank) v[u] = pkt::load(slotOf(ctx, ctx.rank, q0 + u, f.half, false) + first + i);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = q0 + u;
+        if (q >= ctx.world || !ok) break;
+        uint64_t w = mine;
+        if (q != ctx.rank) {
+          w = v[u].data;
+          if (v[u].flag != flag) ok = pkt::read(ctx, slotOf(ctx, ctx.rank, q, f.half, false) + first + i, flag, w, kStatusTimeoutPacket, si, q);
+        }
+        if (ok) accumulate<T, Op>(acc, unpack<T>(w));
+      }
     }
     if (!ok) break;
     const uint64_t out = pack<T>(acc);

@@ -337,11 +337,15 @@ int purlin_collective(PurlinHostContext* h, int collective, const void* src, voi
   const bool variable = isVariable(spec.in);
   if (!variable && bytes == 0) return 0;
   const Policy* forced = static_cast<const Policy*>(policy);
-  // An all-reduce larger than the staging half runs as ONE kernel whose shards stream through per-rank windows of the
-  // staging half under back-pressure (layout.hpp: cyclic composed plan). Should the layout engine refuse (a forced policy
-  // that cannot cycle), it falls back to consecutive segments, each a complete collective on the alternating half.
+  // An all-reduce larger than the staging half can run as ONE kernel whose shards stream through per-rank windows of the
+  // staging half under back-pressure (layout.hpp: cyclic composed plan), or as consecutive segments, each a complete
+  // collective on the alternating half. Measured at 1 GiB, bf16: one kernel 1.03x NCCL at two ranks (segments 1.00x),
+  // but 0.89x at four and 0.77x at eight (segments 0.95x and 0.93x): the windows shrink with the world size. So the
+  // single kernel is the default at two ranks only; PURLIN_AR_SEGMENTS=1 / =0 forces segments / the single kernel.
+  // Should the layout engine refuse the single kernel (a forced policy that cannot cycle), segments run.
   if (spec.type == CollectiveType::allReduce && bytes > h->ws.stagingTRSize) {
-    static const bool segmentsOnly = std::getenv("PURLIN_AR_SEGMENTS") != nullptr;
+    const char* const segEnv = std::getenv("PURLIN_AR_SEGMENTS");   // read per call: such a call moves a gigabyte
+    const bool segmentsOnly = segEnv ? segEnv[0] != '0' : h->dev.world > 2;
     Plan whole;
     if (!segmentsOnly && planFor(spec, h->ws, forced, whole, nullptr)) return launchPlan(h, whole, src, dst, s);
     const size_t seg = roundDown(h->ws.stagingTRSize, size_t(h->dev.world) * kAccessAlign);

@@ -393,6 +393,20 @@ struct Sim {
       case kRolePacketGet: {
         const size_t words = s.bytes / 8;
         const uint64_t flag = flagValue(seq, 0);
+        if (s.peer < 0) {
+          // every peer's packets in one step: the agent walks (peer, word) pairs, peers in ring order
+          const size_t pairs = words * size_t(W - 1);
+          while (a.word < pairs) {
+            const int q = (r + 1 + int(a.word / words)) % W;
+            const size_t i = a.word % words;
+            const HostPacket& pk = slot(r, q, half, (s.flags & kFlagResultHalf) != 0)[s.srcOff / 8 + i];
+            if (pk.flag != flag) return progressed;
+            std::memcpy(R.dst + s.dstOff + size_t(q) * s.bytes + i * 8, &pk.data, 8);
+            ++a.word; progressed = true;
+            if (quantum && ++did >= 64 * quantum && a.word < pairs) return true;
+          }
+          a.done = true; return true;
+        }
         const HostPacket* p = slot(r, s.peer, half, (s.flags & kFlagResultHalf) != 0) + s.srcOff / 8;
         while (a.word < words) {
           if (p[a.word].flag != flag) return progressed;

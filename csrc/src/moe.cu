@@ -29,6 +29,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <string>
 
 #include "purlin/atom.cuh"
@@ -51,12 +52,15 @@ struct PurlinMoeContext {
   const float* topkWeight = nullptr;
   const int32_t* slot = nullptr;
   uint64_t timeoutNs = 0;
+  bool timing = false;                   // PURLIN_MOE_TIMING=1: the kernels stamp their phases (purlin_moe_timing)
 };
 
 namespace {
 
 constexpr int kThreads = 256;
 constexpr int kWarps = kThreads / 32;
+constexpr int kDispatchCtasPerSm = 2;   // the dispatch is bound by memory latency and light on registers: two CTAs of eight warps per SM
+constexpr int kCombineCtasPerSm = 1;    // the weighted sums keep 8 x 32 bytes per lane in flight and need the registers
 constexpr int kMaxExperts = 512;
 constexpr int kChunkRows = 64;          // rows per flag
 constexpr int kMetaWords = 16;          // per staged row: 8 destination rows, 8 gate weights
@@ -82,6 +86,7 @@ struct MoeParams {
   unsigned char* y;                // combine output [tokens, hidden] bf16
   uint64_t* epoch;                 // device call counters: [0] dispatch, [1] combine
   uint32_t* exitCounter;
+  unsigned long long* timing;      // optional (PURLIN_MOE_TIMING=1): per kernel {first start, last sender end, last receiver end, first sender end} in ns
   uint32_t* status;
   uint64_t timeoutNs;
 };
@@ -108,6 +113,19 @@ PURLIN_D bool waitFlag(const MoeParams& p, const uint64_t* flag, uint64_t value,
 
 PURLIN_D uint64_t* dispatchFlag(const MoeParams& p, int onRank, int src, int chunk) { return p.flags[onRank] + p.world + size_t(src) * p.maxChunks + chunk; }
 PURLIN_D uint64_t* combineFlag(const MoeParams& p, int onRank, int from, int chunk) { return p.flags[onRank] + p.world + size_t(p.world + from) * p.maxChunks + chunk; }
+
+// Device-side phase times of one kernel (diagnostics; off unless the context was created with PURLIN_MOE_TIMING=1):
+// every CTA folds its start and the end of its role into four words with atomics.
+PURLIN_D void stampStart(const MoeParams& p, int base) {
+  if (p.timing && threadIdx.x == 0) atomicMin(p.timing + base, (unsigned long long)sig::globalTimerNs());
+}
+PURLIN_D void stampEnd(const MoeParams& p, int base, bool sender) {
+  if (p.timing && threadIdx.x == 0) {
+    const unsigned long long now = sig::globalTimerNs();
+    atomicMax(p.timing + base + (sender ? 1 : 2), now);
+    if (sender) atomicMin(p.timing + base + 3, now);
+  }
+}
 
 // ---------------------------------------------------------------------------------------------
 // route: one warp per token
@@ -168,12 +186,13 @@ PURLIN_D void copyRow(unsigned char* dst, const unsigned char* src, int vecs, in
 // ---------------------------------------------------------------------------------------------
 // dispatch
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_constant__ MoeParams p) {
+__global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(const __grid_constant__ MoeParams p) {
   __shared__ int32_t rowBase[kMaxExperts];      // first row of (this rank, expert e) inside the destination's buffer
   __shared__ int32_t colTotal[kMaxExperts];     // rows of expert e over all ranks
   __shared__ int32_t sendCount[kMaxRanks], recvFrom[kMaxRanks];
   __shared__ int bad;
   const uint64_t epoch = sig::ldRelaxedSys(p.epoch) + 1;
+  stampStart(p, 0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int W = p.world, stride = p.experts + W;
   if (tid == 0) bad = 0;
@@ -326,6 +345,7 @@ __global__ void __launch_bounds__(kThreads, 1) dispatchKernel(const __grid_const
     }
   }
   __syncthreads();
+  stampEnd(p, 0, p.world > 1 && int(blockIdx.x) < (p.senders < int(gridDim.x) ? p.senders : int(gridDim.x) - 1));
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(p.exitCounter, 1u) == gridDim.x - 1) { *p.exitCounter = 0; if (!outOfOrder) *p.epoch = epoch; __threadfence(); }
@@ -344,29 +364,28 @@ PURLIN_D uint32_t packBf16x2(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&b);
 }
 
-// out = sum over the rows named by `mask` of w[k] * rows[k] (fp32 accumulate). 32-byte accesses, two positions of every
-// row in flight per lane (up to 16 loads): the sum is latency-bound otherwise. `mask` is the same in every lane, so the
-// branches are uniform and the arrays stay in registers. rowBytes is a multiple of 32.
-template <int ROWS>
-PURLIN_D void weightedSum(unsigned char* out, const unsigned char* const (&rows)[ROWS], const float (&w)[ROWS], unsigned mask, int vecs32, int lane) {
-  for (int i = lane; i < vecs32; i += 64) {
-    const bool second = i + 32 < vecs32;
-    Vec32 v[2][ROWS];
+// out = sum of w[k] * rows[k] over the first n of R rows (fp32 accumulate). 32-byte accesses, P positions of every row
+// in flight per lane: R x P = 8 loads of 32 bytes, whatever the number of rows, because the sum is latency-bound
+// otherwise (16 in flight spilled).
+// n is the same in every lane, so the branches are uniform and the arrays stay in registers. rowBytes % 32 == 0.
+template <int R, int P>
+PURLIN_D void weightedSum(unsigned char* out, const unsigned char* const (&rows)[8], const float (&w)[8], int n, int vecs32, int lane) {
+  for (int i = lane; i < vecs32; i += 32 * P) {
+    Vec32 v[P][R];
 #pragma unroll
-    for (int k = 0; k < ROWS; ++k)
-      if ((mask >> k) & 1u) {
-        v[0][k] = ld32(rows[k] + size_t(i) * 32);
-        if (second) v[1][k] = ld32(rows[k] + size_t(i + 32) * 32);
-      }
+    for (int h = 0; h < P; ++h)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      if (h == 1 && !second) break;
+      for (int k = 0; k < R; ++k)
+        if (k < n && i + 32 * h < vecs32) v[h][k] = ld32(rows[k] + size_t(i + 32 * h) * 32);
+#pragma unroll
+    for (int h = 0; h < P; ++h) {
+      if (i + 32 * h >= vecs32) break;
       float acc[16];
 #pragma unroll
       for (int j = 0; j < 16; ++j) acc[j] = 0.f;
 #pragma unroll
-      for (int k = 0; k < ROWS; ++k)
-        if ((mask >> k) & 1u) {
+      for (int k = 0; k < R; ++k)
+        if (k < n) {
 #pragma unroll
           for (int j = 0; j < 8; ++j) fmaBf16x2(acc[2 * j], acc[2 * j + 1], v[h][k].x[j], w[k]);
         }
@@ -377,11 +396,18 @@ PURLIN_D void weightedSum(unsigned char* out, const unsigned char* const (&rows)
     }
   }
 }
+// the rows of a sum arrive in arbitrary lanes; few rows take many positions each, many rows few
+PURLIN_D void weightedSumAny(unsigned char* out, const unsigned char* const (&rows)[8], const float (&w)[8], int n, int vecs32, int lane) {
+  if (n <= 2) weightedSum<2, 4>(out, rows, w, n, vecs32, lane);
+  else if (n <= 4) weightedSum<4, 2>(out, rows, w, n, vecs32, lane);
+  else weightedSum<8, 1>(out, rows, w, n, vecs32, lane);
+}
 
-__global__ void __launch_bounds__(kThreads, 1) combineKernel(const __grid_constant__ MoeParams p) {
+__global__ void __launch_bounds__(kThreads, kCombineCtasPerSm) combineKernel(const __grid_constant__ MoeParams p) {
   __shared__ int32_t recvFrom[kMaxRanks];
   __shared__ int bad;
   const uint64_t epoch = sig::ldRelaxedSys(p.epoch + 1) + 1;
+  stampStart(p, 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int W = p.world, stride = p.experts + W;
   if (tid == 0) bad = 0;
@@ -407,18 +433,21 @@ __global__ void __launch_bounds__(kThreads, 1) combineKernel(const __grid_consta
         for (int pp = c * kChunkRows + warp; pp < end; pp += kWarps) {
           const size_t at = size_t(s) * p.maxTokens + pp;
           const int rec = lane < kMetaWords ? p.meta[p.rank][at * kMetaWords + lane] : 0;
+          // lanes 0..7 hold the expert-output rows of this staged row, lanes 8..15 their gate weights; the valid ones are
+          // gathered to the front (j-th valid row = the lane of the j-th set bit)
+          const bool mine = lane < 8 && rec >= 0 && rec < p.capacityRows;
+          const unsigned valid = __ballot_sync(0xffffffffu, mine) & 0xffu;
+          const int n = __popc(valid);
           const unsigned char* rows[8];
           float w[8];
-          unsigned mask = 0;
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            const int r = __shfl_sync(0xffffffffu, rec, k);
-            w[k] = __int_as_float(__shfl_sync(0xffffffffu, rec, 8 + k));
-            const bool valid = r >= 0 && r < p.capacityRows;
-            rows[k] = p.outBuf + size_t(valid ? r : 0) * rowBytes;
-            if (valid) mask |= 1u << k;
+          for (int j = 0; j < 8; ++j) {
+            const int from = j < n ? int(__fns(valid, 0, j + 1)) : 0;
+            const int r = __shfl_sync(0xffffffffu, rec, from);
+            w[j] = __int_as_float(__shfl_sync(0xffffffffu, rec, 8 + from));
+            rows[j] = p.outBuf + size_t(j < n ? r : 0) * rowBytes;
           }
-          weightedSum<8>(p.cbuf[s] + (size_t(p.rank) * p.maxTokens + pp) * rowBytes, rows, w, mask, vecs32, lane);
+          weightedSumAny(p.cbuf[s] + (size_t(p.rank) * p.maxTokens + pp) * rowBytes, rows, w, n, vecs32, lane);
         }
         __syncthreads();
         if (tid == 0) sig::stReleaseSys(combineFlag(p, s, p.rank, c), epoch);
@@ -441,19 +470,21 @@ __global__ void __launch_bounds__(kThreads, 1) combineKernel(const __grid_consta
       if (!__all_sync(0xffffffffu, good)) break;
       __syncwarp();
       const unsigned leaders = __ballot_sync(0xffffffffu, leader) & 0xffu;
+      const int n = __popc(leaders);
       const unsigned char* rows[8];
       float w[8];
 #pragma unroll
-      for (int k = 0; k < 8; ++k) {
-        const int dk = __shfl_sync(0xffffffffu, d, k), pk = __shfl_sync(0xffffffffu, pos, k);
-        const bool use = (leaders >> k) & 1u;
-        rows[k] = p.cbuf[p.rank] + (size_t(use ? dk : 0) * p.maxTokens + (use ? pk : 0)) * rowBytes;
-        w[k] = 1.f;
+      for (int j = 0; j < 8; ++j) {
+        const int from = j < n ? int(__fns(leaders, 0, j + 1)) : 0;
+        const int dk = __shfl_sync(0xffffffffu, d, from), pk = __shfl_sync(0xffffffffu, pos, from);
+        rows[j] = p.cbuf[p.rank] + (size_t(j < n ? dk : 0) * p.maxTokens + (j < n ? pk : 0)) * rowBytes;
+        w[j] = 1.f;
       }
-      weightedSum<8>(p.y + size_t(t) * rowBytes, rows, w, leaders, vecs32, lane);
+      weightedSumAny(p.y + size_t(t) * rowBytes, rows, w, n, vecs32, lane);
     }
   }
   __syncthreads();
+  stampEnd(p, 4, int(blockIdx.x) < senders);
   if (tid == 0) {
     __threadfence();
     if (atomicAdd(p.exitCounter + 1, 1u) == gridDim.x - 1) { p.exitCounter[1] = 0; if (!outOfOrder) p.epoch[1] = epoch; __threadfence(); }
@@ -501,6 +532,7 @@ void fillCommon(MoeParams& p, PurlinMoeContext* c, int tokens) {
   p.epoch = reinterpret_cast<uint64_t*>(lb);
   p.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
   p.status = reinterpret_cast<uint32_t*>(lb + 256);
+  p.timing = c->timing ? reinterpret_cast<unsigned long long*>(lb + 512) : nullptr;
   p.localCounts = reinterpret_cast<uint32_t*>(lb + c->countsLocalOff);
   p.sendList = reinterpret_cast<int32_t*>(lb + c->sendListOff);
   p.pos = reinterpret_cast<int32_t*>(lb + c->posOff);
@@ -552,6 +584,11 @@ PurlinMoeContext* purlin_moe_create(int rank, int world, const uint64_t* peerPtr
   const size_t localBytes = c->posOff + roundUp(size_t(maxTokens) * topk * 4, 1024);
   if (cudaMalloc(&c->local, localBytes) != cudaSuccess) { delete c; setError("cudaMalloc failed"); return nullptr; }
   cudaMemsetAsync(c->local, 0, localBytes, static_cast<cudaStream_t>(stream));
+  if (const char* t = std::getenv("PURLIN_MOE_TIMING"); t && t[0] != '0') {
+    c->timing = true;
+    const unsigned long long fresh[8] = {~0ull, 0, 0, ~0ull, ~0ull, 0, 0, ~0ull};
+    cudaMemcpyAsync(static_cast<unsigned char*>(c->local) + 512, fresh, sizeof(fresh), cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream));
+  }
   cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   return c;
 }
@@ -567,6 +604,27 @@ int purlin_moe_destroy(PurlinMoeContext* c, void* stream) {
 int purlin_moe_status(PurlinMoeContext* c, uint32_t* out4, void* stream) {
   cudaMemcpyAsync(out4, static_cast<unsigned char*>(c->local) + 256, 16, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
   return cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : 1;
+}
+// Phase times of the last dispatch and combine in nanoseconds since each kernel's first CTA started:
+// out8 = {dispatch: last sender end, last receiver end, first sender end, 0, combine: last pusher end, last finisher end,
+// first pusher end, 0}. Synchronises the stream and re-arms the words. Returns 1 when the context was created without
+// PURLIN_MOE_TIMING=1.
+int purlin_moe_timing(PurlinMoeContext* c, uint64_t* out8, void* stream) {
+  if (!c || !c->timing) { setError("timing is off: create the context with PURLIN_MOE_TIMING=1"); return 1; }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  unsigned long long raw[8];
+  unsigned char* at = static_cast<unsigned char*>(c->local) + 512;
+  if (cudaMemcpyAsync(raw, at, sizeof(raw), cudaMemcpyDeviceToHost, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) { setError("reading the timing words failed"); return 1; }
+  for (int k = 0; k < 2; ++k) {
+    const unsigned long long t0 = raw[k * 4];
+    out8[k * 4 + 0] = raw[k * 4 + 1] > t0 ? raw[k * 4 + 1] - t0 : 0;
+    out8[k * 4 + 1] = raw[k * 4 + 2] > t0 ? raw[k * 4 + 2] - t0 : 0;
+    out8[k * 4 + 2] = raw[k * 4 + 3] != ~0ull && raw[k * 4 + 3] > t0 ? raw[k * 4 + 3] - t0 : 0;
+    out8[k * 4 + 3] = 0;
+  }
+  const unsigned long long fresh[8] = {~0ull, 0, 0, ~0ull, ~0ull, 0, 0, ~0ull};
+  if (cudaMemcpyAsync(at, fresh, sizeof(fresh), cudaMemcpyHostToDevice, s) != cudaSuccess || cudaStreamSynchronize(s) != cudaSuccess) { setError("re-arming the timing words failed"); return 1; }
+  return 0;
 }
 int purlin_moe_clear_status(PurlinMoeContext* c, void* stream) {
   return cudaMemsetAsync(static_cast<unsigned char*>(c->local) + 256, 0, 16, static_cast<cudaStream_t>(stream)) == cudaSuccess ? 0 : 1;
@@ -608,7 +666,7 @@ int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const in
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.x = static_cast<const unsigned char*>(x); p.sentRow = sentRow; p.recvCounts = recvCounts;
-  const int grid = smCount();
+  const int grid = smCount() * kDispatchCtasPerSm;
   // remote stores fill the links with far fewer CTAs (about 32 GB/s each) than the local fan-out needs for HBM
   p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(std::min(grid / 3, 32), 1);
   dispatchKernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
@@ -626,7 +684,7 @@ int purlin_moe_combine(PurlinMoeContext* c, void* y, int tokens, const int32_t* 
   MoeParams p{};
   fillCommon(p, c, tokens);
   p.y = static_cast<unsigned char*>(y);
-  const int grid = smCount();
+  const int grid = smCount() * kCombineCtasPerSm;
   // the pushers read every expert output row; the finishers add at most `world` rows per token
   p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(grid * 2 / 3, 1);
   combineKernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);

@@ -124,7 +124,10 @@ class CpuContext:
                     seam = torch.zeros(seam_extent, dtype=torch.uint8)
                     seam[s.seamOff:seam_extent] = out
             elif s.role == _native.ROLE_PACKET_GET and not (s.flags & _native.FLAG_RESULT_HALF):
-                d8[s.dstOff:s.dstOff + s.bytes] = packet_from(s.peer, s.srcOff, s.bytes)
+                # peer -1: the packets of every peer in one step, slice q at dstOff + q * bytes
+                for q in ([s.peer] if s.peer >= 0 else [q for q in range(W) if q != r]):
+                    at = s.dstOff + (q * s.bytes if s.peer < 0 else 0)
+                    d8[at:at + s.bytes] = packet_from(q, s.srcOff, s.bytes)
             elif s.role == _native.ROLE_PACKET_REDUCE:
                 parts = [s8[s.seamOff:s.seamOff + s.bytes] if q == r else packet_from(q, s.srcOff, s.bytes) for q in range(W)]
                 out = self._reduce(parts, dtype, op)
@@ -140,5 +143,7 @@ class CpuContext:
         peers_res = self._exchange(mine, mine.numel())
         for s in steps:
             if s.role == _native.ROLE_PACKET_GET and (s.flags & _native.FLAG_RESULT_HALF):
-                d8[s.dstOff:s.dstOff + s.bytes] = peers_res[s.peer][s.srcOff:s.srcOff + s.bytes]
+                for q in ([s.peer] if s.peer >= 0 else [q for q in range(W) if q != r]):
+                    at = s.dstOff + (q * s.bytes if s.peer < 0 else 0)
+                    d8[at:at + s.bytes] = peers_res[q][s.srcOff:s.srcOff + s.bytes]
         self.seq += 1

@@ -10,6 +10,7 @@ token, already weighted and summed over its local experts.  The reference offers
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -33,6 +34,7 @@ def _lib():
         lib.purlin_moe_destroy.argtypes = [vp, vp]
         lib.purlin_moe_status.argtypes = [vp, C.POINTER(C.c_uint32), vp]
         lib.purlin_moe_clear_status.argtypes = [vp, vp]
+        lib.purlin_moe_timing.argtypes = [vp, C.POINTER(u64), vp]
         lib.purlin_moe_recv_buffer.restype = vp
         lib.purlin_moe_recv_buffer.argtypes = [vp]
         lib.purlin_moe_out_buffer.restype = vp
@@ -104,7 +106,10 @@ class ExpertParallelContext:
         return self.topk_idx[:t], self.topk_weight[:t]
 
     def dispatch(self, x: torch.Tensor, blocks: int = 0):
-        """Sends every token to its experts' GPUs; returns (rows in expert-major order, rows per local expert)."""
+        """Sends every token to its experts' GPUs; returns (rows in expert-major order, rows per local expert).
+        ``blocks`` > 0 sets the number of sending CTAs (the rest of the grid copies rows to their expert rows);
+        ``PURLIN_MOE_SENDERS`` in the environment sets the default."""
+        blocks = blocks or int(os.environ.get("PURLIN_MOE_SENDERS", 0))
         t = x.shape[0]
         if x.dtype != torch.bfloat16 or not x.is_contiguous() or x.shape[1] != self.hidden:
             raise ValueError("x must be contiguous bf16 [tokens, hidden]")
@@ -121,6 +126,9 @@ class ExpertParallelContext:
         return self._out
 
     def combine(self, tokens: int, out: Optional[torch.Tensor] = None, blocks: int = 0) -> torch.Tensor:
+        """``blocks`` > 0 sets the number of CTAs that form and push the per-GPU partial sums (the rest add the rows that
+        arrive); ``PURLIN_MOE_PUSHERS`` in the environment sets the default."""
+        blocks = blocks or int(os.environ.get("PURLIN_MOE_PUSHERS", 0))
         if out is None:
             out = torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=self.device)
         rc = self.lib.purlin_moe_combine(self.ctx, out.data_ptr(), tokens, self.topk_idx.data_ptr(), self.topk_weight.data_ptr(),
@@ -137,6 +145,16 @@ class ExpertParallelContext:
                     7: "an expert id outside [0, experts)", 9: "dispatch called twice without a combine in between",
                     10: "combine called without a matching dispatch"}.get(out[1], "bad plan") if out[0] == 6 else "a wait timed out"
             raise RuntimeError(f"purlin: MoE exchange failed: {what} (where {out[1]}, peer {out[2]})")
+
+    def timing(self):
+        """Device-side phase times in microseconds since the previous call of this method (contexts created with
+        ``PURLIN_MOE_TIMING=1``): from the first CTA's start to the last sender / last receiver / first sender leaving the
+        dispatch, and the same for the pushers and finishers of the combine. Synchronises the stream."""
+        out = (C.c_uint64 * 8)()
+        _native.check(self.lib, self.lib.purlin_moe_timing(self.ctx, out, self.stream()))
+        us = [v / 1e3 for v in out]
+        return {"dispatch": {"last_sender": us[0], "last_receiver": us[1], "first_sender": us[2]},
+                "combine": {"last_pusher": us[4], "last_finisher": us[5], "first_pusher": us[6]}}
 
     def close(self):
         if self.ctx:

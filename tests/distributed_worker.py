@@ -95,6 +95,7 @@ def main():
                 ("staged composed chunked", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=256 << 10), 3 << 20),
                 ("segmented", dict(arPath=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=1 << 20), staging * 2 + W * 32 * 8)]
     for name, kw, n in ([] if subset else ar_cases):
+        os.environ["PURLIN_AR_SEGMENTS"] = "1" if name == "segmented" else "0"     # the default depends on the world size
         for dtype in (0, 4, 1):
             case(f"AR {name} dt{dtype}", AR, nbytes=n, dtype=dtype, pol=policy(**kw))
         case(f"AR {name} max", AR, nbytes=n, dtype=0, op=2, pol=policy(**kw))
@@ -123,9 +124,11 @@ def main():
             case(f"{cname} budget 64 CTAs {n}", coll, nbytes=n, dtype=0, reps=1)
     purlin.set_max_ctas(old_budget)
     # an all-reduce beyond the staging size is one kernel; here with the reduction done by the switch
+    os.environ["PURLIN_AR_SEGMENTS"] = "0"
     if mc and not subset:
         case("AR cyclic nvls", AR, nbytes=staging * 2 + W * 32 * 8, dtype=0,
              pol=policy(arPath=1, memType=1, consumeBlocks=16, putBlocks=8, gatherBlocks=8, chunkBytes=1 << 20))
+    os.environ.pop("PURLIN_AR_SEGMENTS", None)
     case("AR default graph", AR, nbytes=64 << 10, dtype=0, reps=1, graph=True)
     case("AR default graph large", AR, nbytes=2 << 20, dtype=0, reps=1, graph=True)
     # variable-length

@@ -254,3 +254,24 @@ def test_variable_length_forms_borrow_measured_bands(world):
                     assert torch.equal(outs[r].view(torch.uint8), exp[r].view(torch.uint8)), f"coll {coll} world {world} scale {scale} rank {r}"
     finally:
         tuning.clear()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8, 16])
+def test_latency_plans_fetch_all_peers_in_one_step(world):
+    # fixed-size forms: ONE get step for the packets of every peer (slices of equal size at q * bytes), so a rank polls its
+    # peers at the same time; the variable-length forms keep one step per peer (their slices differ)
+    for coll, nbytes in ((AG, 4096), (A2A, 4096), (AR, 4096 * world)):
+        plan, _ = P.build_plan(coll, world, 1, nbytes, policy=policy(regime=0, arPath=1))
+        gets = [s for s in plan.active_steps() if s.role == _native.ROLE_PACKET_GET]
+        assert len(gets) == 1 and gets[0].peer == -1 and gets[0].seamOff == 1
+        assert gets[0].bytes == 4096 and gets[0].dstOff == 0
+    sizes = [64 * (q + 1) for q in range(world)]
+    plan, _ = P.build_plan(AGV, world, 1, 0, sizes=sizes, policy=policy(regime=0))
+    gets = [s for s in plan.active_steps() if s.role == _native.ROLE_PACKET_GET]
+    assert len(gets) == world - 1 and all(s.peer >= 0 for s in gets)
+    # the interpreter runs the fused step on every rank
+    for coll in (AG, A2A, AR):
+        status, outs, exp = sim(coll, world, nbytes=2048 * world if coll == AR else 2048, dtype=4, policy=policy(regime=0, arPath=1))
+        assert status[0] == 0
+        for o, e in zip(outs, exp):
+            assert torch.equal(o.view(torch.uint8), e.view(torch.uint8))
