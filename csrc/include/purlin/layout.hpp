@@ -544,11 +544,19 @@ inline bool buildLatencyPlan(const CollectiveSpec& spec, const Policy& pol, cons
     if (mc) p.flags |= kFlagMulticastOut;
     if (!one(p)) return false;
   } else {
-    for (int k = 1; k < W; ++k) {
-      const int d = (r + k) % W;
-      if (pt.send[d] > cap) { err = "payload exceeds the packet slot"; return false; }
-      Step p{}; p.role = kRolePacketPut; p.peer = d; p.srcOff = pt.sendOff[d]; p.dstOff = 0; p.bytes = pt.send[d];
+    for (int k = 1; k < W; ++k) if (pt.send[(r + k) % W] > cap) { err = "payload exceeds the packet slot"; return false; }
+    if (equalSlices(pt.sendOff, pt.send)) {
+      // one step sends every peer its slice: a thread loads one word and stores it once, instead of W - 1 steps whose
+      // loads wait for the stores of the step before
+      Step p{}; p.role = kRolePacketPut; p.peer = -1; p.flags |= kFlagScatter;
+      p.srcOff = pt.sendOff[r] - size_t(r) * pt.send[r]; p.dstOff = 0; p.bytes = pt.send[r]; p.seamOff = uint64_t(r);
       if (!one(p)) return false;
+    } else {
+      for (int k = 1; k < W; ++k) {
+        const int d = (r + k) % W;
+        Step p{}; p.role = kRolePacketPut; p.peer = d; p.srcOff = pt.sendOff[d]; p.dstOff = 0; p.bytes = pt.send[d];
+        if (!one(p)) return false;
+      }
     }
   }
   if (!reduce) {

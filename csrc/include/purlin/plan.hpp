@@ -35,7 +35,8 @@ enum Role : int32_t {
   kRoleConsume = 2,   // wait signals[rank][peer]; peer staging -> user dst
   kRoleReduce = 3,    // wait signals[rank][*]; reduce every rank's staging -> dst and/or seam
   kRoleGather = 4,    // composed tail: wait gatherSignals[rank][peer]; peer seam -> user dst
-  kRolePacketPut = 5, // latency: user src words -> packets in peer's slot (-1: every peer)
+  kRolePacketPut = 5, // latency: user src words -> packets in peer's slot (-1: every peer; with kFlagScatter peer q gets
+                      // its own slice, the `bytes` at srcOff + q * bytes)
   kRolePacketGet = 6, // latency: packets from `peer` in own slot -> user dst. peer -1: from every peer q, `bytes` each, to
                       // dstOff + q * bytes (equal slices; seamOff holds this rank's index, whose slice is not touched)
   kRolePacketReduce = 7,  // latency: reduce own words with every peer's packets -> dst (+ publish)
@@ -55,6 +56,7 @@ enum StepFlags : uint32_t {
   kFlagDrainGather = 1u << 10, // cyclic stage of a composed all-reduce: a peer's window is free again once that peer has
                                // published the reduced chunk (gatherSignals); this rank's own window, which doubles as the
                                // seam, once every peer has gathered the reduced chunk out of it (consumedSignals)
+  kFlagScatter = 1u << 11,     // packet put to every peer: peer q receives slice q of the source (equal slices), not the same words
 };
 
 struct Step {

@@ -119,7 +119,9 @@ inline std::string checkPlan(const Plan& plan, int world, const WorkspaceLayout&
       const size_t words = s.bytes / 8;
       switch (s.role) {
         case kRolePacketPut:
-          if (!detail::within(s.srcOff, s.bytes, ext.srcBytes)) return bad(i, "source", s.srcOff, s.bytes, ext.srcBytes);
+          if ((s.flags & kFlagScatter) && (s.peer >= 0 || s.seamOff >= uint64_t(world))) return bad(i, "scattered put needs peer -1 and the own slice index", s.seamOff, 1, size_t(world));
+          if (!detail::within(s.srcOff, (s.flags & kFlagScatter) ? s.bytes * size_t(world) : s.bytes, ext.srcBytes))
+            return bad(i, "source", s.srcOff, (s.flags & kFlagScatter) ? s.bytes * size_t(world) : s.bytes, ext.srcBytes);
           if (!detail::within(s.dstOff * 2, words * 16, slotBytes)) return bad(i, "packet slot (put)", s.dstOff * 2, words * 16, slotBytes);
           break;
         case kRolePacketGet:

@@ -267,6 +267,16 @@ PURLIN_D void packetPut(const Context& ctx, const Step& s, const Frame& f) {
   const uint64_t* src = reinterpret_cast<const uint64_t*>(f.src + s.srcOff);
   const uint64_t flag = flagValue(f.seq, 0);
   const size_t first = s.dstOff / 8;
+  if (s.flags & kFlagScatter) {
+    // every peer gets its own slice: (peer, word) pairs over the threads, one load and one store each
+    const size_t pairs = words * size_t(ctx.world - 1);
+    for (size_t idx = size_t(f.bIdx - s.blockBegin) * blockDim.x + threadIdx.x; idx < pairs; idx += stride) {
+      const size_t i = idx % words;
+      const int d = (ctx.rank + 1 + int(idx / words)) % ctx.world;
+      pkt::write(slotOf(ctx, d, ctx.rank, f.half, false) + first + i, src[size_t(d) * words + i], flag);
+    }
+    return;
+  }
   if (s.peer < 0 && !(s.flags & kFlagMulticastOut) && ctx.world > 2 && words * size_t(ctx.world - 1) <= 2 * stride) {
     // Peer-striped: with few words and many peers, (word, peer) pairs are spread over the threads, so that every
     // store to a peer is some thread's first and only one instead of the last of W - 1 issued in a row

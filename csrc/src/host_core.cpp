@@ -384,6 +384,14 @@ struct Sim {
         const size_t words = s.bytes / 8;
         const uint64_t flag = flagValue(seq, 0);
         for (size_t i = 0; i < words; ++i) {
+          if (s.flags & kFlagScatter) {      // peer q receives slice q of the source
+            for (int q = 0; q < W; ++q) {
+              if (q == r) continue;
+              uint64_t v; std::memcpy(&v, R.src + s.srcOff + size_t(q) * s.bytes + i * 8, 8);
+              slot(q, r, half, false)[s.dstOff / 8 + i] = HostPacket{v, flag};
+            }
+            continue;
+          }
           uint64_t v; std::memcpy(&v, R.src + s.srcOff + i * 8, 8);
           if (s.peer >= 0) slot(s.peer, r, half, false)[s.dstOff / 8 + i] = HostPacket{v, flag};
           else for (int q = 0; q < W; ++q) { if (q == r && !(s.flags & kFlagMulticastOut)) continue; slot(q, r, half, false)[s.dstOff / 8 + i] = HostPacket{v, flag}; }

@@ -86,6 +86,7 @@ struct MoeParams {
   unsigned char* y;                // combine output [tokens, hidden] bf16
   uint64_t* epoch;                 // device call counters: [0] dispatch, [1] combine
   uint32_t* exitCounter;
+  uint32_t* work;                  // next item of {dispatch senders, dispatch receivers, combine pushers}; the last CTA out clears them
   unsigned long long* timing;      // optional (PURLIN_MOE_TIMING=1): per kernel {first start, last sender end, last receiver end, first sender end} in ns
   uint32_t* status;
   uint64_t timeoutNs;
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
   __shared__ int32_t rowBase[kMaxExperts];      // first row of (this rank, expert e) inside the destination's buffer
   __shared__ int32_t colTotal[kMaxExperts];     // rows of expert e over all ranks
   __shared__ int32_t sendCount[kMaxRanks], recvFrom[kMaxRanks];
-  __shared__ int bad;
+  __shared__ int bad, nextItem;
   const uint64_t epoch = sig::ldRelaxedSys(p.epoch) + 1;
   stampStart(p, 0);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -266,15 +267,25 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
       const int wBits = __shfl_sync(0xffffffffu, __float_as_int(w), lane & 7);
       return lane < 8 ? row : (lane < 16 && (lane - 8) < p.topk ? wBits : 0);
     };
+    // Items (a chunk of one peer's list) are handed out through a counter, in list order: a CTA that finishes early takes
+    // the next one, so the CTAs of a role end together whatever the number of items per CTA would have been (with a
+    // static split of 174 items over 32 CTAs the last CTA ran a fifth longer than the first, and everybody waited).
+    // `want` is the same in every thread of the CTA and only grows, so the walk over the items below is done once.
+    auto grab = [&](uint32_t* counter) {
+      __syncthreads();
+      if (tid == 0) nextItem = int(atomicAdd(counter, 1u));
+      __syncthreads();
+      return nextItem;
+    };
     if (int(blockIdx.x) < senders) {
       // 4a. sender: chunks of the send lists of the other ranks, destinations interleaved so that every link is busy.
       // A token's row crosses NVLink once per destination, with the record that tells the receiver where it belongs.
-      int item = 0;
+      int item = 0, want = grab(p.work + 0);
       for (int c = 0; c < p.maxChunks; ++c) {
         for (int dd = 0; dd + 1 < W; ++dd) {
           const int d = (p.rank + 1 + dd) % W;
           if (c * kChunkRows >= sendCount[d]) continue;
-          if (item++ % senders != int(blockIdx.x)) continue;
+          if (item++ != want) continue;
           const int end = min((c + 1) * kChunkRows, sendCount[d]);
           for (int pp = c * kChunkRows + warp; pp < end; pp += kWarps) {
             const int t = p.sendList[size_t(d) * p.maxTokens + pp];
@@ -283,21 +294,21 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
             if (lane < kMetaWords) p.meta[d][(size_t(p.rank) * p.maxTokens + pp) * kMetaWords + lane] = rec;
             copyRow(p.stage[d] + (size_t(p.rank) * p.maxTokens + pp) * rowBytes, p.x + size_t(t) * rowBytes, vecs, lane);
           }
-          __syncthreads();
+          want = grab(p.work + 0);      // (its first barrier also orders the rows before the flag)
+          // the release waits for this CTA's remote stores; only thread 0's warp waits with it
           if (tid == 0) sig::stReleaseSys(dispatchFlag(p, d, p.rank, c), epoch);
         }
       }
     } else {
       // 4b. receiver: every row that belongs on this rank goes to its expert rows (local traffic). Rows of this rank's
       // own tokens come straight from x; a peer's rows are copied out of the staging area as its chunks land.
-      const int nRecv = int(gridDim.x) - senders, me = int(blockIdx.x) - senders;
-      int item = 0;
+      int item = 0, want = grab(p.work + 1);
       for (int c = 0; c < p.maxChunks && ok; ++c) {
         for (int ss = 0; ss < W && ok; ++ss) {
           const int s = (p.rank + W - ss) % W;          // own rows first, then the rank that serves this one first
           const int count = s == p.rank ? sendCount[s] : recvFrom[s];
           if (c * kChunkRows >= count) continue;
-          if (item++ % nRecv != me) continue;
+          if (item++ != want) continue;
           if (s != p.rank) {
             int good = 1;
             if (tid == 0) good = waitFlag(p, dispatchFlag(p, p.rank, s, c), epoch, 3, s) ? 1 : 0;
@@ -340,6 +351,7 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
                 }
             }
           }
+          want = grab(p.work + 1);
         }
       }
     }
@@ -348,7 +360,7 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
   stampEnd(p, 0, p.world > 1 && int(blockIdx.x) < (p.senders < int(gridDim.x) ? p.senders : int(gridDim.x) - 1));
   if (tid == 0) {
     __threadfence();
-    if (atomicAdd(p.exitCounter, 1u) == gridDim.x - 1) { *p.exitCounter = 0; if (!outOfOrder) *p.epoch = epoch; __threadfence(); }
+    if (atomicAdd(p.exitCounter, 1u) == gridDim.x - 1) { *p.exitCounter = 0; p.work[0] = 0; p.work[1] = 0; if (!outOfOrder) *p.epoch = epoch; __threadfence(); }
   }
 }
 
@@ -405,7 +417,7 @@ PURLIN_D void weightedSumAny(unsigned char* out, const unsigned char* const (&ro
 
 __global__ void __launch_bounds__(kThreads, kCombineCtasPerSm) combineKernel(const __grid_constant__ MoeParams p) {
   __shared__ int32_t recvFrom[kMaxRanks];
-  __shared__ int bad;
+  __shared__ int bad, nextItem;
   const uint64_t epoch = sig::ldRelaxedSys(p.epoch + 1) + 1;
   stampStart(p, 4);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -417,18 +429,27 @@ __global__ void __launch_bounds__(kThreads, kCombineCtasPerSm) combineKernel(con
   if (outOfOrder && tid == 0) { bad = 1; reportBad(p, 10, 0); }
   if (tid < W) recvFrom[tid] = int(p.countsAll[p.rank][size_t(tid) * stride + p.experts + p.rank]);
   __syncthreads();
-  bool ok = !bad && sig::ldRelaxedGpu32(p.status) == 0u;
+  const bool ok = __syncthreads_and(!bad && sig::ldRelaxedGpu32(p.status) == 0u) != 0;   // one answer for the whole CTA: the roles below hold barriers
   const int vecs32 = p.hiddenBytes / 32;
   const size_t rowBytes = size_t(p.hiddenBytes);
   const int senders = p.senders < int(gridDim.x) ? p.senders : int(gridDim.x) - 1;
   if (ok && int(blockIdx.x) < senders) {
-    // A. pusher: for every row staged here by rank s, the gate-weighted sum of its expert outputs goes home as ONE row
-    int item = 0;
+    // A. pusher: for every row staged here by rank s, the gate-weighted sum of its expert outputs goes home as ONE row.
+    // Items (one chunk of one source) are handed out through a counter in chunk order: the pushers end together, and the
+    // chunks complete in the order in which the finishers at home need them (a static split of 232 items over 98 CTAs
+    // had the last pusher end at 313 us and the first at 187 us, and left a third of the finishers' work for the end).
+    auto grab = [&]() {
+      __syncthreads();
+      if (tid == 0) nextItem = int(atomicAdd(p.work + 2, 1u));
+      __syncthreads();
+      return nextItem;
+    };
+    int item = 0, want = grab();
     for (int c = 0; c < p.maxChunks; ++c) {
       for (int ss = 0; ss < W; ++ss) {
         const int s = (p.rank + 1 + ss) % W;
         if (c * kChunkRows >= recvFrom[s]) continue;
-        if (item++ % senders != int(blockIdx.x)) continue;
+        if (item++ != want) continue;
         const int end = min((c + 1) * kChunkRows, recvFrom[s]);
         for (int pp = c * kChunkRows + warp; pp < end; pp += kWarps) {
           const size_t at = size_t(s) * p.maxTokens + pp;
@@ -449,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, kCombineCtasPerSm) combineKernel(con
           }
           weightedSumAny(p.cbuf[s] + (size_t(p.rank) * p.maxTokens + pp) * rowBytes, rows, w, n, vecs32, lane);
         }
-        __syncthreads();
+        want = grab();                  // (its first barrier also orders the rows before the flag)
         if (tid == 0) sig::stReleaseSys(combineFlag(p, s, p.rank, c), epoch);
       }
     }
@@ -487,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, kCombineCtasPerSm) combineKernel(con
   stampEnd(p, 4, int(blockIdx.x) < senders);
   if (tid == 0) {
     __threadfence();
-    if (atomicAdd(p.exitCounter + 1, 1u) == gridDim.x - 1) { p.exitCounter[1] = 0; if (!outOfOrder) p.epoch[1] = epoch; __threadfence(); }
+    if (atomicAdd(p.exitCounter + 1, 1u) == gridDim.x - 1) { p.exitCounter[1] = 0; p.work[2] = 0; if (!outOfOrder) p.epoch[1] = epoch; __threadfence(); }
   }
 }
 
@@ -531,6 +552,7 @@ void fillCommon(MoeParams& p, PurlinMoeContext* c, int tokens) {
   p.outBuf = c->peers[c->rank] + c->outOff;
   p.epoch = reinterpret_cast<uint64_t*>(lb);
   p.exitCounter = reinterpret_cast<uint32_t*>(lb + 64);
+  p.work = reinterpret_cast<uint32_t*>(lb + 128);
   p.status = reinterpret_cast<uint32_t*>(lb + 256);
   p.timing = c->timing ? reinterpret_cast<unsigned long long*>(lb + 512) : nullptr;
   p.localCounts = reinterpret_cast<uint32_t*>(lb + c->countsLocalOff);
@@ -668,7 +690,7 @@ int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const in
   p.x = static_cast<const unsigned char*>(x); p.sentRow = sentRow; p.recvCounts = recvCounts;
   const int grid = smCount() * kDispatchCtasPerSm;
   // remote stores fill the links with far fewer CTAs (about 32 GB/s each) than the local fan-out needs for HBM
-  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(std::min(grid / 3, 32), 1);
+  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(std::min(grid / 3, 48), 1);
   dispatchKernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { setError(std::string("dispatch launch: ") + cudaGetErrorString(e)); return 1; }

@@ -18,7 +18,7 @@ K_MAX_STEPS = 56
 ROLE_NAMES = ["stage", "local", "consume", "reduce", "gather", "packet_put", "packet_get", "packet_reduce"]
 FLAG_TO_SEAM, FLAG_TO_DST, FLAG_MULTIMEM_LOAD, FLAG_MULTICAST_OUT = 1, 2, 4, 8
 FLAG_LOCAL_SOURCE, FLAG_CYCLIC, FLAG_PUBLISH, FLAG_RESULT_HALF = 16, 32, 64, 128
-FLAG_NOTIFY_GATHER, FLAG_DRAIN_SELF = 256, 512
+FLAG_NOTIFY_GATHER, FLAG_DRAIN_SELF, FLAG_DRAIN_GATHER, FLAG_SCATTER = 256, 512, 1024, 2048
 (ROLE_STAGE, ROLE_LOCAL, ROLE_CONSUME, ROLE_REDUCE, ROLE_GATHER,
  ROLE_PACKET_PUT, ROLE_PACKET_GET, ROLE_PACKET_REDUCE) = range(8)
 

@@ -96,7 +96,8 @@ class CpuContext:
                 tr[s.dstOff:s.dstOff + s.bytes] = s8[s.srcOff:s.srcOff + s.bytes]
             elif s.role == _native.ROLE_PACKET_PUT:
                 for d in (range(W) if s.peer < 0 else [s.peer]):
-                    lr[d * stride + s.dstOff: d * stride + s.dstOff + s.bytes] = s8[s.srcOff:s.srcOff + s.bytes]
+                    at = s.srcOff + (d * s.bytes if s.flags & _native.FLAG_SCATTER else 0)     # scatter: peer d gets slice d
+                    lr[d * stride + s.dstOff: d * stride + s.dstOff + s.bytes] = s8[at:at + s.bytes]
             elif s.role == _native.ROLE_LOCAL:
                 d8[s.dstOff:s.dstOff + s.bytes] = s8[s.srcOff:s.srcOff + s.bytes]
         # every rank performs every exchange, whatever its own plan holds, so the group calls always match

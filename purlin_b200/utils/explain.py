@@ -20,7 +20,7 @@ from purlin_b200.utils.bench import parse_size
 
 ROLES = ["stage", "local", "consume", "reduce", "gather", "packet-put", "packet-get", "packet-reduce"]
 FLAGS = ["to-seam", "to-dst", "multimem-load", "multicast-out", "local-source", "cyclic", "publish", "result-half", "notify-gather",
-         "drain-self"]
+         "drain-self", "drain-gather", "scatter"]
 KINDS = {"all_reduce": 0, "all_gather": 1, "all_gather_v": 2, "reduce_scatter": 3, "reduce_scatter_v": 4, "all_to_all": 5, "all_to_all_v": 6}
 
 

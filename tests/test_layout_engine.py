@@ -265,12 +265,20 @@ def test_latency_plans_fetch_all_peers_in_one_step(world):
         gets = [s for s in plan.active_steps() if s.role == _native.ROLE_PACKET_GET]
         assert len(gets) == 1 and gets[0].peer == -1 and gets[0].seamOff == 1
         assert gets[0].bytes == 4096 and gets[0].dstOff == 0
+    # ... and ONE put step where every peer gets its own slice (all-to-all, reduce-scatter, the scatter half of a two-shot all-reduce)
+    for coll, nbytes in ((A2A, 4096), (RS, 4096), (AR, 4096 * world)):
+        plan, _ = P.build_plan(coll, world, 1, nbytes, policy=policy(regime=0, arPath=1))
+        puts = [s for s in plan.active_steps() if s.role == _native.ROLE_PACKET_PUT]
+        assert len(puts) == 1 and puts[0].peer == -1 and puts[0].flags & _native.FLAG_SCATTER and puts[0].seamOff == 1
+        assert puts[0].bytes == 4096 and puts[0].srcOff == 0
+    puts = [s for s in P.build_plan(AG, world, 1, 4096, policy=policy(regime=0))[0].active_steps() if s.role == _native.ROLE_PACKET_PUT]
+    assert len(puts) == 1 and not puts[0].flags & _native.FLAG_SCATTER          # the same words to everyone
     sizes = [64 * (q + 1) for q in range(world)]
     plan, _ = P.build_plan(AGV, world, 1, 0, sizes=sizes, policy=policy(regime=0))
     gets = [s for s in plan.active_steps() if s.role == _native.ROLE_PACKET_GET]
     assert len(gets) == world - 1 and all(s.peer >= 0 for s in gets)
     # the interpreter runs the fused step on every rank
-    for coll in (AG, A2A, AR):
+    for coll in (AG, A2A, RS, AR):
         status, outs, exp = sim(coll, world, nbytes=2048 * world if coll == AR else 2048, dtype=4, policy=policy(regime=0, arPath=1))
         assert status[0] == 0
         for o, e in zip(outs, exp):
