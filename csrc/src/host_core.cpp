@@ -106,6 +106,16 @@ static bool buildWithinBudget(const CollectiveSpec& s, Policy& p, const Workspac
 bool planFor(const CollectiveSpec& s, const WorkspaceLayout& ws, const Policy* forced, Plan& plan, Policy* chosen) {
   std::string err;
   Policy p = forced ? *forced : selectPolicy(s, ws);
+  if (!forced && p.regime == int32_t(Regime::latency) && !isVariable(s.in) && !isVariable(s.out) && s.world > 1) {
+    // The put and get steps of the fixed-size latency plans spread (peer, word) pairs over the threads. A measured band
+    // may name fewer CTAs than one pair per thread needs (at these sizes the sweep that wrote it could not tell 1 CTA
+    // from 16: 11 - 12 us either way in stream mode), and then a thread walks its pairs one memory round trip after the
+    // other. Up to 16 CTAs, give every pair its own thread.
+    const uint64_t pairs = dispatchBytes(s) / 8 * uint64_t(s.world - 1);
+    const uint64_t threads = uint64_t(p.threads > 0 ? p.threads : 256);
+    const int floorBlocks = int(std::min<uint64_t>(16, (pairs + threads - 1) / threads));
+    if (p.lrBlocks < floorBlocks) p.lrBlocks = floorBlocks;
+  }
   bool ok = buildWithinBudget(s, p, ws, plan, err);
   if (!ok && !forced) {   // a measured band may not fit this call (uneven V sizes): fall back to built-in choices
     std::string err2;

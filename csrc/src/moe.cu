@@ -689,8 +689,9 @@ int purlin_moe_dispatch(PurlinMoeContext* c, const void* x, int tokens, const in
   fillCommon(p, c, tokens);
   p.x = static_cast<const unsigned char*>(x); p.sentRow = sentRow; p.recvCounts = recvCounts;
   const int grid = smCount() * kDispatchCtasPerSm;
-  // remote stores fill the links with far fewer CTAs (about 32 GB/s each) than the local fan-out needs for HBM
-  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(std::min(grid / 3, 48), 1);
+  // remote stores fill the links with far fewer CTAs (about 32 GB/s each) than the local fan-out needs for HBM; the
+  // receivers end last (4 GPUs, 296 CTAs: 32 senders 352 us, 48 senders 357 - 372 us, 64 senders 363 us)
+  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(std::min(grid / 3, 32), 1);
   dispatchKernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { setError(std::string("dispatch launch: ") + cudaGetErrorString(e)); return 1; }
@@ -707,8 +708,10 @@ int purlin_moe_combine(PurlinMoeContext* c, void* y, int tokens, const int32_t* 
   fillCommon(p, c, tokens);
   p.y = static_cast<unsigned char*>(y);
   const int grid = smCount() * kCombineCtasPerSm;
-  // the pushers read every expert output row; the finishers add at most `world` rows per token
-  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(grid * 2 / 3, 1);
+  // The pushers read every expert output row, the finishers add at most `world` rows per token, and it is the finishers
+  // that end last: measured at 4 GPUs (4096 tokens, hidden 7168, top-8 of 256), 80 pushers of 148 CTAs 343 us, 98 pushers
+  // 366 us, 110 pushers 392 us.
+  p.senders = blocks > 0 ? std::min(blocks, grid - 1) : std::max(grid * 54 / 100, 1);
   combineKernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) { setError(std::string("combine launch: ") + cudaGetErrorString(e)); return 1; }
