@@ -91,10 +91,12 @@ def buffer_type(t: torch.dtype) -> DataType:
 class ContextHandle:
     """Everything one process group needs: the native context, the symmetric block and its rendezvous handle."""
     __slots__ = ("mod", "ctx", "buf", "hdl", "sig_buf", "sig_hdl", "v_sig_buf", "v_sig_hdl",
-                 "rank", "world", "device", "group", "staging_size", "cpu", "layout")
+                 "rank", "world", "device", "group", "staging_size", "cpu", "layout", "call_fixed")
 
     def __init__(self, mod, ctx, buf, hdl, rank, world, device, group, staging_size, layout, cpu=None):
         self.mod, self.ctx, self.buf, self.hdl = mod, ctx, buf, hdl
+        # the entry point of the launch-bound path: the C extension when it loads, else the ctypes function
+        self.call_fixed = _native.fast_call_fixed(mod) if cpu is None and hasattr(mod, "purlin_call_fixed") else None
         # the reference keeps three symmetric tensors; here all regions live in one block, these are views of it
         self.sig_buf = self.sig_hdl = self.v_sig_buf = self.v_sig_hdl = None
         self.rank, self.world, self.device, self.group = rank, world, device, group
@@ -256,10 +258,9 @@ def _call_fixed(handle, collective: int, src, dst, nbytes: int, traits: int, str
         return _call(handle, collective, src, dst, nbytes, None, None, traits & 0xff, (traits >> 8) & 0xff, traits >> 16, stream_ptr, policy)
     if not (src.is_contiguous() and dst.is_contiguous()):
         raise ValueError("purlin collectives need contiguous tensors")
-    mod = handle.mod
-    if mod.purlin_call_fixed(handle.ctx, collective, src.data_ptr(), dst.data_ptr(), nbytes, traits,
-                             stream_ptr if stream_ptr is not None else _stream(None)):
-        _native.check(mod, 1)
+    if handle.call_fixed(handle.ctx, collective, src.data_ptr(), dst.data_ptr(), nbytes, traits,
+                         stream_ptr if stream_ptr is not None else _stream(None)):
+        _native.check(handle.mod, 1)
 
 
 _AR, _AG, _RS, _A2A = int(Collective.ALL_REDUCE), int(Collective.ALL_GATHER), int(Collective.REDUCE_SCATTER), int(Collective.ALL_TO_ALL)
@@ -276,10 +277,21 @@ def all_gather_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, strea
     _call(handle, Collective.ALL_GATHER_V, in_tensor, out_tensor, 0, list(bytes_list), None, 0, 0, 0, stream_ptr, policy)
 
 
+_TRAITS = {}       # (torch dtype, op, reduction mode) -> dtype | op << 8 | mode << 16, computed once per combination
+
+
+def _traits(dtype, op, reduction_mode) -> int:
+    key = (dtype, op, reduction_mode)
+    t = _TRAITS.get(key)
+    if t is None:
+        t = _TRAITS[key] = int(buffer_type(dtype)) | (int(op) << 8) | (_mode(reduction_mode) << 16)
+    return t
+
+
 def all_reduce(in_tensor, out_tensor, handle, stream_ptr=None, reduction_mode=ReductionMode.NON_DETERMINISTIC,
                op: ReduceOp = ReduceOp.ADD, policy=None):
     _call_fixed(handle, _AR, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size(),
-                int(buffer_type(in_tensor.dtype)) | (int(op) << 8) | (_mode(reduction_mode) << 16), stream_ptr, policy)
+                _traits(in_tensor.dtype, op, reduction_mode), stream_ptr, policy)
 
 
 def all_to_all(in_tensor, out_tensor, handle, stream_ptr=None, policy=None):
@@ -299,7 +311,7 @@ def all_to_all_v(in_tensor, out_tensor, splits: Sequence[int], handle, stream_pt
 def reduce_scatter(in_tensor, out_tensor, handle, stream_ptr=None, reduction_mode=ReductionMode.NON_DETERMINISTIC,
                    op: ReduceOp = ReduceOp.ADD, policy=None):
     _call_fixed(handle, _RS, in_tensor, out_tensor, in_tensor.numel() * in_tensor.element_size() // handle.world,
-                int(buffer_type(in_tensor.dtype)) | (int(op) << 8) | (_mode(reduction_mode) << 16), stream_ptr, policy)
+                _traits(in_tensor.dtype, op, reduction_mode), stream_ptr, policy)
 
 
 def reduce_scatter_v(in_tensor, out_tensor, bytes_list: Sequence[int], handle, stream_ptr=None,

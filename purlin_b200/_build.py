@@ -160,6 +160,23 @@ def build_cuda(force: bool = False, verbose: bool = False, ptxas_info: bool = Fa
         flags, force, verbose)
 
 
+def fastcall_name() -> str:
+    import sysconfig
+    return "_purlin_fastcall" + (sysconfig.get_config_var("EXT_SUFFIX") or ".so")
+
+
+def build_fastcall(force: bool = False, verbose: bool = False) -> Path:
+    """The CPython extension of the launch-bound call path (csrc/src/fastcall.c); it links against nothing but libc."""
+    import sysconfig
+    src = CSRC / "src" / "fastcall.c"
+    flags = ["-O2", "-fPIC", "-Wall", "-I", sysconfig.get_paths()["include"]]
+    return _build_one(
+        fastcall_name(), [src],
+        lambda s, o: ["gcc", *flags, "-c", str(s), "-o", str(o)],
+        lambda objs, out: ["gcc", "-shared", "-o", str(out), *map(str, objs)],
+        flags, force, verbose)
+
+
 def build_cpp_tests(force: bool = False, verbose: bool = False, folder: str = "tests"):
     """The C++ test binaries (csrc/tests) or example programs (csrc/examples), linked against the in-tree libpurlin_cuda.so."""
     lib = build_cuda(force, verbose)
@@ -203,7 +220,7 @@ def build_examples(force: bool = False, verbose: bool = False):
 
 
 def build_all(force: bool = False, verbose: bool = False):
-    return (build_host(force, verbose), build_cuda(force, verbose), *build_cpp_tests(force, verbose),
+    return (build_host(force, verbose), build_cuda(force, verbose), build_fastcall(force, verbose), *build_cpp_tests(force, verbose),
             *build_examples(force, verbose), *build_cpu_tests(force, verbose))
 
 

@@ -147,6 +147,30 @@ def cuda():
     return _cuda
 
 
+_fastcall = None
+
+
+def fast_call_fixed(lib):
+    """``purlin_call_fixed`` of ``lib`` behind a CPython extension that takes the seven scalars as they are (a third of
+    the per-call cost of the ctypes foreign call); the ctypes function itself when the extension cannot be built or loaded
+    (``PURLIN_NO_FASTCALL=1`` forces that). One library per process is bound; a second one gets the ctypes function."""
+    global _fastcall
+    if os.environ.get("PURLIN_NO_FASTCALL") or not isinstance(lib, C.CDLL):
+        return lib.purlin_call_fixed
+    if _fastcall is None:
+        try:
+            import importlib.util
+            path = _resolve(_build.fastcall_name(), _build.build_fastcall)
+            spec = importlib.util.spec_from_file_location("_purlin_fastcall", str(path))
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            mod.bind(C.cast(lib.purlin_call_fixed, C.c_void_p).value)
+            _fastcall = (lib, mod)
+        except Exception:
+            _fastcall = (None, None)
+    return _fastcall[1].call_fixed if _fastcall[0] is lib else lib.purlin_call_fixed
+
+
 def last_error(lib) -> str:
     return (lib.purlin_last_error() or b"").decode()
 

@@ -5,6 +5,7 @@ element types, context, stream and reduction mode; initialize asks the provider 
 and forwards the multicast pointer; finalize is idempotent; non-contiguous tensors and bad modes are rejected.
 """
 import ctypes as C
+import os
 
 import pytest
 import torch
@@ -245,3 +246,41 @@ def test_plan_explainer_prints_roles_and_regions(capsys):
         assert explain.main(["all_gather_v", "--world", "4", "--gpu", ""]) == 2      # sizes are required
     finally:
         tuning.clear()
+
+
+def test_fastcall_extension_passes_the_seven_scalars_unchanged():
+    """The CPython extension of the launch-bound path: arguments arrive as given (pointers beyond 2^63 included), the
+    status comes back, and the loader binds it to the real library (whose answer to a null context is an error, no GPU needed)."""
+    import ctypes as C
+    import importlib.util
+    from purlin_b200 import _build
+    path = _build.build_fastcall()
+    spec = importlib.util.spec_from_file_location("_purlin_fastcall", str(path))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    with pytest.raises(RuntimeError):
+        mod.call_fixed(1, 2, 3, 4, 5, 6, 7)                                   # nothing bound yet
+    seen = []
+    proto = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_uint, C.c_void_p)
+
+    def target(ctx, collective, src, dst, nbytes, traits, stream):
+        seen.append((ctx, collective, src, dst, nbytes, traits, stream))
+        return 7 if collective == 5 else 0
+    cb = proto(target)
+    mod.bind(C.cast(cb, C.c_void_p).value)
+    big = (1 << 64) - 32
+    assert mod.call_fixed(0xC0FFEE, 3, big, 0x7F0000001000, 1 << 40, (1 << 16) | (2 << 8) | 4, 0xABCDEF) == 0
+    assert seen[-1] == (0xC0FFEE, 3, big, 0x7F0000001000, 1 << 40, (1 << 16) | (2 << 8) | 4, 0xABCDEF)
+    assert mod.call_fixed(1, 5, 0, 0, 0, 0, 0) == 7
+    assert seen[-1][2] is None and seen[-1][6] is None                        # null pointers stay null
+    with pytest.raises(TypeError):
+        mod.call_fixed(1, 2, 3)
+    with pytest.raises((TypeError, OverflowError)):
+        mod.call_fixed(1, 2, 3, 4, -1, 6, 7)                                  # a negative byte count is refused, not wrapped
+    # the loader: bound to the library itself
+    from purlin_b200 import _native
+    lib = _native.cuda()
+    fast = _native.fast_call_fixed(lib)
+    assert fast is not lib.purlin_call_fixed or os.environ.get("PURLIN_NO_FASTCALL")
+    assert fast(0, 0, 0, 0, 64, 4, 0) == 1
+    assert "null context" in _native.last_error(lib)
