@@ -63,6 +63,7 @@ constexpr int kDispatchCtasPerSm = 2;   // the dispatch is bound by memory laten
 constexpr int kCombineCtasPerSm = 1;    // the weighted sums keep 8 x 32 bytes per lane in flight and need the registers
 constexpr int kMaxExperts = 512;
 constexpr int kChunkRows = 64;          // rows per flag
+constexpr int kRecvRows = 16;           // rows per receiver item of the dispatch (a part of a chunk)
 constexpr int kMetaWords = 16;          // per staged row: 8 destination rows, 8 gate weights
 
 struct MoeParams {
@@ -308,50 +309,56 @@ __global__ void __launch_bounds__(kThreads, kDispatchCtasPerSm) dispatchKernel(c
           const int s = (p.rank + W - ss) % W;          // own rows first, then the rank that serves this one first
           const int count = s == p.rank ? sendCount[s] : recvFrom[s];
           if (c * kChunkRows >= count) continue;
-          if (item++ != want) continue;
-          if (s != p.rank) {
-            int good = 1;
-            if (tid == 0) good = waitFlag(p, dispatchFlag(p, p.rank, s, c), epoch, 3, s) ? 1 : 0;
-            ok = __syncthreads_and(good) != 0;
-            if (!ok) break;
+          // A receiver's item is a part of a chunk (kRecvRows rows, two per warp): a whole chunk per CTA left most CTAs
+          // without work (4096 local rows are 64 chunks for 296 CTAs) and made the last chunk to land a 50 us tail.
+          for (int part = 0; part < kChunkRows / kRecvRows && ok; ++part) {
+            const int begin = c * kChunkRows + part * kRecvRows;
+            if (begin >= count) break;
+            if (item++ != want) continue;
+            if (s != p.rank) {
+              int good = 1;
+              if (tid == 0) good = waitFlag(p, dispatchFlag(p, p.rank, s, c), epoch, 3, s) ? 1 : 0;
+              ok = __syncthreads_and(good) != 0;
+              if (!ok) break;
+            }
+            const int end = min(begin + kRecvRows, count);
+            for (int pp = begin + warp; pp < end; pp += kWarps) {
+              const size_t at = size_t(s) * p.maxTokens + pp;
+              int row;
+              const unsigned char* src;
+              if (s == p.rank) {
+                const int t = p.sendList[size_t(s) * p.maxTokens + pp];
+                const int rec = recordOf(t, s, row);
+                if (lane < kMetaWords) p.meta[s][at * kMetaWords + lane] = rec;      // the combine reads it like a peer's
+                src = p.x + size_t(t) * rowBytes;
+              } else {
+                row = lane < 8 ? p.meta[p.rank][at * kMetaWords + lane] : -1;
+                src = p.stage[p.rank] + at * rowBytes;
+              }
+              // the row is read once and written to each of its expert rows
+              unsigned char* dst[8];
+              unsigned mask = 0;
+  #pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int r = __shfl_sync(0xffffffffu, row, k);
+                const bool valid = r >= 0 && r < p.capacityRows;
+                dst[k] = p.recvBuf + size_t(valid ? r : 0) * rowBytes;
+                if (valid) mask |= 1u << k;
+              }
+              for (int i = lane; i < vecs; i += 32 * 8) {
+                Vec32 v[8];
+  #pragma unroll
+                for (int u = 0; u < 8; ++u) if (i + u * 32 < vecs) v[u] = ld32(src + size_t(i + u * 32) * 32);
+  #pragma unroll
+                for (int k = 0; k < 8; ++k)
+                  if ((mask >> k) & 1u) {
+  #pragma unroll
+                    for (int u = 0; u < 8; ++u) if (i + u * 32 < vecs) st32(dst[k] + size_t(i + u * 32) * 32, v[u]);
+                  }
+              }
+            }
+            want = grab(p.work + 1);
           }
-          const int end = min((c + 1) * kChunkRows, count);
-          for (int pp = c * kChunkRows + warp; pp < end; pp += kWarps) {
-            const size_t at = size_t(s) * p.maxTokens + pp;
-            int row;
-            const unsigned char* src;
-            if (s == p.rank) {
-              const int t = p.sendList[size_t(s) * p.maxTokens + pp];
-              const int rec = recordOf(t, s, row);
-              if (lane < kMetaWords) p.meta[s][at * kMetaWords + lane] = rec;      // the combine reads it like a peer's
-              src = p.x + size_t(t) * rowBytes;
-            } else {
-              row = lane < 8 ? p.meta[p.rank][at * kMetaWords + lane] : -1;
-              src = p.stage[p.rank] + at * rowBytes;
-            }
-            // the row is read once and written to each of its expert rows
-            unsigned char* dst[8];
-            unsigned mask = 0;
-#pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              const int r = __shfl_sync(0xffffffffu, row, k);
-              const bool valid = r >= 0 && r < p.capacityRows;
-              dst[k] = p.recvBuf + size_t(valid ? r : 0) * rowBytes;
-              if (valid) mask |= 1u << k;
-            }
-            for (int i = lane; i < vecs; i += 32 * 8) {
-              Vec32 v[8];
-#pragma unroll
-              for (int u = 0; u < 8; ++u) if (i + u * 32 < vecs) v[u] = ld32(src + size_t(i + u * 32) * 32);
-#pragma unroll
-              for (int k = 0; k < 8; ++k)
-                if ((mask >> k) & 1u) {
-#pragma unroll
-                  for (int u = 0; u < 8; ++u) if (i + u * 32 < vecs) st32(dst[k] + size_t(i + u * 32) * 32, v[u]);
-                }
-            }
-          }
-          want = grab(p.work + 1);
         }
       }
     }
