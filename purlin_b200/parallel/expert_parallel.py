@@ -5,7 +5,7 @@ One layer is: ``route`` -> ``dispatch`` -> experts work on ``recv_rows()`` and w
 ``dispatch`` and ``combine`` must alternate on one stream (a call out of order is refused on the device and
 ``check()`` raises).  A token crosses NVLink once per destination GPU in each direction, however many of that GPU's
 experts it was routed to: the receiver fans it out to its expert rows, and the experts' GPU sends back one row per
-token, already weighted and summed over its local experts.  The reference offers allToAllV only; BASELINE configuration 4 asks for this fusion.
+token, already weighted and summed over its local experts.  The reference offers allToAllV only; a MoE layer needs the exchange fused with the permute and the weighted sum.
 """
 from __future__ import annotations
 

@@ -3,8 +3,8 @@
 ``TensorParallelContext`` owns the symmetric buffers of the fused kernels (csrc/src/gemm_sm100.cu):
   * ``ag_gemm``  : all-gather of sequence-sharded activations fused into the GEMM that consumes them
   * ``gemm_rs``  : GEMM whose output tiles are reduce-scattered by sequence from the epilogue
-The reference offers only the separate collectives (allGather, reduceScatter); BASELINE configuration 5 asks for
-the fusion.  With a world of one the same tcgen05 kernel runs without its communication warps.
+The reference offers only the separate collectives (allGather, reduceScatter; csrc/include/purlin/host/allGather.cuh,
+reduceScatter.cuh of the reference); a tensor-parallel layer wants the transfer hidden under the math.  With a world of one the same tcgen05 kernel runs without its communication warps.
 """
 from __future__ import annotations
 
